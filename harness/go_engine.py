@@ -194,6 +194,18 @@ class BlockManager:  # block_manager.go:41-263
                 self.hash_to_block_id[h] = block_id
             seq.block_table.append(block_id)
 
+    def reserve(self, seq: Sequence, num_tokens: int):
+        """Blocks for a sequence that is handed over in portions: grow its table to hold
+        num_tokens tokens.  No hashes are published (the tokens of a block may not all be known
+        yet), so these blocks are never offered as a cached prefix."""
+        need = (num_tokens + self.block_size - 1) // self.block_size - len(seq.block_table)
+        if need > len(self.free_block_ids):
+            raise RuntimeError("out of cache blocks")
+        for _ in range(max(0, need)):
+            block_id = self.free_block_ids[0]
+            self._allocate_block(block_id)
+            seq.block_table.append(block_id)
+
     def deallocate(self, seq: Sequence):  # :206-219
         for block_id in reversed(seq.block_table):
             block = self.blocks[block_id]

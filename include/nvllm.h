@@ -179,6 +179,57 @@ int nvllm_tp_unique_id(uint8_t out_id[128]);
  * (tensor_model_runner.go:21-32) together with set_weight/finalize. */
 int nvllm_create(const nvllm_config* cfg, const uint8_t* tp_id, nvllm_handle** out);
 
+/* ---- models given as a list of layers ------------------------------------
+ * A model whose config.json lists its layers one by one (each with its own mixer and
+ * feed-forward sizes) is created from an array of nvllm_layer_spec instead of the uniform
+ * fields of nvllm_config.  Every layer is a parallel block: h = LayerNorm(x) (weight, no
+ * additive term), x += mixer(h) + feed_forward(h).  Tensors are handed in by checkpoint name
+ * (nvllm_set_named_weight, or nvllm_load_safetensors with NVLLM_ARCH_DUGOPEL). */
+enum nvllm_mixer_kind { NVLLM_MIXER_LATENT_ATTENTION = 1 };
+enum nvllm_mlp_kind { NVLLM_MLP_NONE = 0, NVLLM_MLP_DENSE = 1, NVLLM_MLP_MOE = 2 };
+
+typedef struct nvllm_layer_spec {
+  int32_t mixer;        /* nvllm_mixer_kind */
+  /* latent attention: queries through a q_rank latent; keys / values through a kv_rank latent
+   * plus one rotated key part of rot_dim shared by the heads.  Per head: dim unrotated and
+   * rot_dim rotated query / key entries, vdim value entries. */
+  int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank;
+  int32_t rot_dims;     /* leading entries of the rotated part that are rotated (<= rot_dim, even) */
+  int32_t kv_from;      /* -1: own key/value down projection and cache; j: reads layer j's cache */
+  float rot_base;
+  float scale;          /* multiplies the scores */
+  int32_t mlp;          /* nvllm_mlp_kind */
+  int32_t ff;           /* inner size of the dense feed-forward / of one expert */
+  float limit;          /* clamp of the gated unit */
+  int32_t experts, top; /* MoE: experts, experts per token */
+  int32_t groups, keep_groups; /* MoE: equal groups of neighbouring experts, groups a token may use */
+  float router_scale;   /* MoE: weights = softmax scores of the chosen experts * router_scale */
+} nvllm_layer_spec;
+
+typedef struct nvllm_layered_config {
+  int32_t abi_version;  /* = NVLLM_ABI_VERSION */
+  int32_t vocab_size, hidden, num_layers;
+  float norm_eps;
+  float embedding_scale;   /* x = embed[token] * embedding_scale */
+  float logit_softcap;     /* logits <- cap * tanh(logits / cap); 0 = none */
+  int32_t precision;       /* nvllm_precision */
+  int32_t num_kv_blocks, max_num_seqs, max_batched_tokens, device;
+} nvllm_layered_config;
+
+int nvllm_create_layered(const nvllm_layered_config* cfg, const nvllm_layer_spec* layers,
+                         nvllm_handle** out);
+
+/* One tensor of a layered model by its checkpoint name ("embed", "l3.mix.uq", "l1.mlp.e2.gate",
+ * "final.norm", "head", ...), in the checkpoint's layout (linears [out, in]).  The shape is checked. */
+int nvllm_set_named_weight(nvllm_handle* h, const char* name, int dtype, const void* host_data,
+                           const int64_t* shape, int ndim);
+
+/* Ask the NEXT nvllm_run for the logits of further rows besides each sequence's last one.
+ * rows[i] indexes the step's computed tokens in order (the new tokens of sequence 0, then of
+ * sequence 1, ...).  After that run, nvllm_fetch_logits copies them out as [n_rows, V]. */
+int nvllm_request_logits(nvllm_handle* h, const int32_t* rows, int n_rows);
+int nvllm_fetch_logits(nvllm_handle* h, float* out, int n_rows);
+
 /* Hybrid models (ModelConfig.HybridLayers, config.go:113): types[l] = 1 makes layer l a Mamba2
  * block (norm -> Mamba2 -> residual, norm -> FFN -> residual; generic_model.go:162-202), 0 an
  * attention block.  Call before the first nvllm_set_weight; needs the mamba_* config fields. */
@@ -194,7 +245,8 @@ enum nvllm_arch {
   NVLLM_ARCH_GPT2 = 0,        /* GetGPT2Mapping: Conv1D [in,out] tensors, fused c_attn */
   NVLLM_ARCH_FALCON = 1,      /* GetFalconMapping: fused query_key_value, parallel block */
   NVLLM_ARCH_LLAMA = 2,       /* GetLlamaMapping: separate q/k/v, gate_proj + up_proj */
-  NVLLM_ARCH_GRANITE_MOE = 3  /* GetGraniteMoEMapping: router + stacked expert tensors */
+  NVLLM_ARCH_GRANITE_MOE = 3, /* GetGraniteMoEMapping: router + stacked expert tensors */
+  NVLLM_ARCH_DUGOPEL = 4      /* layered handle: every tensor of the file by its own name */
 };
 
 /* Load every weight of the model straight from `model_dir` — model.safetensors, or the shards

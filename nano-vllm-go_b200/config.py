@@ -11,7 +11,10 @@ Llama-3.2 shapes are the HF config.json values the reference reads at load
 from __future__ import annotations
 
 import ctypes
+import json
+import os
 from dataclasses import dataclass, replace
+from typing import Optional, Tuple
 
 ABI_VERSION = 1
 KV_BLOCK_SIZE = 256  # nanovllm/sequence.go:52
@@ -23,7 +26,9 @@ ACT_GELU, ACT_SWIGLU = 0, 1
 BLOCK_SEQUENTIAL, BLOCK_PARALLEL = 0, 1
 PREC_FP32, PREC_BF16 = 0, 1
 # enum nvllm_arch (checkpoint families of generic_loader.go:60-182)
-ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE = 0, 1, 2, 3
+ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL = 0, 1, 2, 3, 4
+MIXER_LATENT_ATTENTION = 1
+MLP_NONE, MLP_DENSE, MLP_MOE = 0, 1, 2
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 
 # enum nvllm_weight_id
@@ -275,3 +280,176 @@ PRESETS = {
     "granite-moe-1b": granite_moe_1b,
     "falcon-7b": falcon_7b,
 }
+
+
+# ---- models given as a list of layers (include/nvllm.h: nvllm_layer_spec) ----------------
+
+class CLayerSpec(ctypes.Structure):
+    """``struct nvllm_layer_spec``."""
+
+    _fields_ = [
+        ("mixer", ctypes.c_int32),
+        ("heads", ctypes.c_int32), ("dim", ctypes.c_int32), ("rot_dim", ctypes.c_int32),
+        ("vdim", ctypes.c_int32), ("kv_rank", ctypes.c_int32), ("q_rank", ctypes.c_int32),
+        ("rot_dims", ctypes.c_int32), ("kv_from", ctypes.c_int32),
+        ("rot_base", ctypes.c_float), ("scale", ctypes.c_float),
+        ("mlp", ctypes.c_int32), ("ff", ctypes.c_int32), ("limit", ctypes.c_float),
+        ("experts", ctypes.c_int32), ("top", ctypes.c_int32),
+        ("groups", ctypes.c_int32), ("keep_groups", ctypes.c_int32),
+        ("router_scale", ctypes.c_float),
+    ]
+
+
+class CLayeredConfig(ctypes.Structure):
+    """``struct nvllm_layered_config``."""
+
+    _fields_ = [
+        ("abi_version", ctypes.c_int32), ("vocab_size", ctypes.c_int32), ("hidden", ctypes.c_int32),
+        ("num_layers", ctypes.c_int32), ("norm_eps", ctypes.c_float),
+        ("embedding_scale", ctypes.c_float), ("logit_softcap", ctypes.c_float),
+        ("precision", ctypes.c_int32), ("num_kv_blocks", ctypes.c_int32),
+        ("max_num_seqs", ctypes.c_int32), ("max_batched_tokens", ctypes.c_int32),
+        ("device", ctypes.c_int32),
+    ]
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: a latent-attention mixer and its feed-forward (none, dense, or MoE)."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    rot_base: float
+    rot_dims: int
+    scale: float
+    kv_from: int = -1
+    mixer: int = MIXER_LATENT_ATTENTION
+    mlp: int = MLP_NONE
+    ff: int = 0
+    limit: float = 0.0
+    experts: int = 0
+    top: int = 0
+    groups: int = 0
+    keep_groups: int = 0
+    router_scale: float = 1.0
+
+    def to_c(self) -> CLayerSpec:
+        c = CLayerSpec()
+        for name, _ in CLayerSpec._fields_:
+            setattr(c, name, getattr(self, name))
+        return c
+
+    def tensor_shapes(self, layer: int, width: int) -> dict:
+        """Checkpoint names and shapes of this layer's tensors (linears [out, in])."""
+        p = f"l{layer}."
+        d = {p + "norm1": (width,),
+             p + "mix.dq": (self.q_rank, width), p + "mix.dq.norm": (self.q_rank,),
+             p + "mix.uq": (self.heads * (self.dim + self.rot_dim), self.q_rank),
+             p + "mix.uk": (self.heads * self.dim, self.kv_rank),
+             p + "mix.uv": (self.heads * self.vdim, self.kv_rank),
+             p + "mix.g": (self.heads, width), p + "mix.o": (width, self.heads * self.vdim)}
+        if self.kv_from < 0:
+            d[p + "mix.dkv"] = (self.kv_rank + self.rot_dim, width)
+            d[p + "mix.dkv.norm"] = (self.kv_rank,)
+        if self.mlp == MLP_DENSE:
+            d.update({p + "mlp.gate": (self.ff, width), p + "mlp.up": (self.ff, width),
+                      p + "mlp.down": (width, self.ff)})
+        elif self.mlp == MLP_MOE:
+            d[p + "mlp.router"] = (self.experts, width)
+            for e in range(self.experts):
+                d.update({f"{p}mlp.e{e}.gate": (self.ff, width), f"{p}mlp.e{e}.up": (self.ff, width),
+                          f"{p}mlp.e{e}.down": (width, self.ff)})
+        return d
+
+
+@dataclass(frozen=True)
+class ListedModelConfig:
+    """A model whose config.json lists its layers (architecture "Dugopel")."""
+    name: str
+    vocab_size: int
+    hidden: int
+    layers: Tuple[LayerSpec, ...]
+    norm_eps: float
+    embedding_scale: float = 1.0
+    logit_softcap: float = 0.0
+    eos_token_id: int = -1
+    arch: int = ARCH_DUGOPEL
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    def tensor_shapes(self) -> dict:
+        d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,),
+             "head": (self.vocab_size, self.hidden)}
+        for i, l in enumerate(self.layers):
+            d.update(l.tensor_shapes(i, self.hidden))
+        return d
+
+    def matmul_params(self) -> int:
+        return sum(a * b for (a, *r) in [s for s in self.tensor_shapes().values() if len(s) == 2]
+                   for b in r) - self.vocab_size * self.hidden
+
+    def cache_bytes_per_token(self, bytes_per_el: int = 2) -> int:
+        return sum((l.kv_rank + l.rot_dim) * bytes_per_el for l in self.layers if l.kv_from < 0)
+
+    def to_c(self, precision: int, num_kv_blocks: int = -1, max_num_seqs: int = 512,
+             max_batched_tokens: int = 16384, device: int = 0):
+        c = CLayeredConfig()
+        c.abi_version = ABI_VERSION
+        c.vocab_size, c.hidden, c.num_layers = self.vocab_size, self.hidden, len(self.layers)
+        c.norm_eps, c.embedding_scale, c.logit_softcap = self.norm_eps, self.embedding_scale, self.logit_softcap
+        c.precision, c.num_kv_blocks = precision, num_kv_blocks
+        c.max_num_seqs, c.max_batched_tokens, c.device = max_num_seqs, max_batched_tokens, device
+        specs = (CLayerSpec * len(self.layers))(*[l.to_c() for l in self.layers])
+        return c, specs
+
+
+def _dugopel_layer(i: int, lc: dict) -> LayerSpec:
+    if lc.get("type") != "latent_attention":
+        raise ValueError(f"layer {i}: unknown layer type {lc.get('type')!r}")
+    m = lc["mixer"]
+    kw = dict(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
+              kv_rank=int(m["kv_rank"]), q_rank=int(m["q_rank"]), rot_base=float(m["rot"]["base"]),
+              rot_dims=int(m["rot"]["dims"]), scale=float(m["scale"]),
+              kv_from=int(m["kv_from"]) if m.get("kv_from") is not None else -1)
+    mlp = lc.get("mlp")
+    if mlp is None:
+        pass
+    elif mlp["kind"] == "dense":
+        kw.update(mlp=MLP_DENSE, ff=int(mlp["ff"]), limit=float(mlp["limit"]))
+    elif mlp["kind"] == "moe":
+        r = mlp["router"]
+        g = r.get("groups") or {}
+        kw.update(mlp=MLP_MOE, ff=int(mlp["expert"]["ff"]), limit=float(mlp["expert"]["limit"]),
+                  experts=int(r["experts"]), top=int(r["top"]), groups=int(g.get("count", 0)),
+                  keep_groups=int(g.get("keep", 0)), router_scale=float(r.get("scale", 1.0)))
+    else:
+        raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+    return LayerSpec(**kw)
+
+
+def dugopel_from_json(j: dict) -> ListedModelConfig:
+    """config.json of the Dugopel design: every size and constant comes from the file."""
+    return ListedModelConfig(
+        name="dugopel", vocab_size=int(j["vocab"]), hidden=int(j["width"]),
+        layers=tuple(_dugopel_layer(i, lc) for i, lc in enumerate(j["layers"])),
+        norm_eps=float(j["norm"]["eps"]), embedding_scale=float(j["embedding"]["scale"]),
+        logit_softcap=float(j.get("logit_softcap") or 0.0))
+
+
+# model registry: config.json "architecture" -> config builder
+ARCHITECTURES = {"Dugopel": dugopel_from_json}
+
+
+def from_model_dir(model_dir: str):
+    """The model class a directory's config.json names."""
+    with open(os.path.join(model_dir, "config.json")) as f:
+        j = json.load(f)
+    arch = j.get("architecture")
+    if arch not in ARCHITECTURES:
+        raise ValueError(f"config.json names architecture {arch!r}; known: {sorted(ARCHITECTURES)}")
+    return ARCHITECTURES[arch](j)

@@ -1,0 +1,424 @@
+// attention_latent.cu — latent ("compressed key/value") attention over the paged pool.
+//
+// A layer of this kind caches, per token, ONE row shared by all heads: the normed latent
+// c [R] followed by the rotated key part k_r [rot]  (Dk = R + rot).  Per head the key is
+// [W_uk c | k_r] and the value W_uv c.  The kernels never expand keys or values: with
+// q~ = W_uk^T q_n  (absorbed query, R wide) the score is (q~ . c + q_r . k_r) * scale, and the
+// head's output is W_uv (sum_j p_j c_j) — i.e. multi-query attention with one latent "kv head"
+// whose key row is [c | k_r] and whose value row is the first R entries of the same row.
+//
+//  latent_prep_kernel     sums the split-K partials of the fused input projection
+//                         [W_dq | W_dkv | W_g] h, RMS-norms the query latent, RMS-norms the key
+//                         latent and rotates the shared key part into the pool row at slots[t],
+//                         and keeps sigmoid(W_g h) per head
+//  rope_table_kernel      cos / sin of pos * base^(-2i/dims) for the step's rows (double)
+//  latent_q_kernel        q = W_uq c_q (split-K partials) -> [q_n W_uk | rope(q_r)] per head
+//  latent_attn_kernel     causal online-softmax attention of (query, head) items against the
+//                         latent rows; one warp per item, a CTA's items share each key tile;
+//                         optional key splits (decode) merged by latent_combine_kernel
+//  latent_out_kernel      head output = gate * W_uv (sum p c), written as the O projection's input
+// All arithmetic is fp32 (double for the angles); QT / KT are the activation / cache dtypes.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nvllm {
+
+constexpr int LAT_WARPS = 8;    // (query, head) items per attention CTA
+constexpr int LAT_KT = 32;      // keys per shared-memory tile: one per lane
+constexpr int LAT_NACC = 16;    // accumulator registers per lane: R <= 32 * LAT_NACC
+
+// ---------------------------------------------------------------- rope table
+__global__ void rope_table_kernel(const int* __restrict__ positions, int T, int half,
+                                  const double* __restrict__ inv_freq, float* __restrict__ cosT,
+                                  float* __restrict__ sinT) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int t = i / half, j = i % half;
+  double s, c;
+  sincos((double)positions[t] * inv_freq[j], &s, &c);
+  cosT[i] = (float)c;
+  sinT[i] = (float)s;
+}
+cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int half,
+                              const double* inv_freq, float* cosT, float* sinT) {
+  if (T <= 0 || half <= 0) return cudaSuccess;
+  const int n = T * half;
+  (void)launch_k(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, st, positions, T, half, inv_freq,
+                 cosT, sinT);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- input-projection epilogue
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(256) latent_prep_kernel(LatentArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float row[];  // [n_in]
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int n_in = a.q_rank + (a.own_kv ? a.R + a.rot : 0) + a.H;
+  pdl_wait();
+  for (int i = threadIdx.x; i < n_in; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < a.in_S; k++) s += a.in_p[(size_t)k * a.in_stride + (size_t)t * a.in_ld + i];
+    row[i] = s;
+  }
+  __syncthreads();
+  // query latent: c_q = v / sqrt(mean(v^2) + eps) * w
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.q_rank; i += blockDim.x) ss += row[i] * row[i];
+  ss = block_sum(ss, red);
+  const float inv_q = 1.0f / sqrtf(ss / (float)a.q_rank + a.eps);
+  QT* cq = (QT*)a.cq + (size_t)t * a.q_rank_p;
+  for (int i = threadIdx.x; i < a.q_rank_p; i += blockDim.x)
+    cq[i] = from_f32<QT>(i < a.q_rank ? row[i] * inv_q * a.dq_norm[i] : 0.f);
+  if (a.own_kv) {
+    const float* v = row + a.q_rank;
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) s2 += v[i] * v[i];
+    s2 = block_sum(s2, red);
+    const float inv_k = 1.0f / sqrtf(s2 / (float)a.R + a.eps);
+    KT* pr = (KT*)a.pool + (size_t)a.slots[t] * (a.R + a.rot);
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) pr[i] = from_f32<KT>(v[i] * inv_k * a.dkv_norm[i]);
+    // shared key part: entry i pairs with i + half inside the first rot_dims entries
+    const float* kr = v + a.R;
+    const int half = a.rot_dims / 2;
+    for (int i = threadIdx.x; i < a.rot; i += blockDim.x) {
+      float o = kr[i];
+      if (i < half) {
+        const float c = a.cosT[(size_t)t * half + i], s = a.sinT[(size_t)t * half + i];
+        o = kr[i] * c - kr[i + half] * s;
+      } else if (i < a.rot_dims) {
+        const int j = i - half;
+        const float c = a.cosT[(size_t)t * half + j], s = a.sinT[(size_t)t * half + j];
+        o = kr[i] * c + kr[j] * s;
+      }
+      pr[a.R + i] = from_f32<KT>(o);
+    }
+  }
+  const float* g = row + a.q_rank + (a.own_kv ? a.R + a.rot : 0);
+  for (int i = threadIdx.x; i < a.H; i += blockDim.x) a.gate[(size_t)t * a.H + i] = 1.0f / (1.0f + expf(-g[i]));
+}
+
+cudaError_t launch_latent_prep(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  const size_t smem = (size_t)(a.q_rank + a.R + a.rot + a.H) * sizeof(float);
+  if (qdt == DT_F32 && kvdt == DT_F32)
+    (void)launch_k(latent_prep_kernel<float, float>, dim3(a.T), dim3(256), smem, st, a);
+  else if (qdt == DT_BF16 && kvdt == DT_BF16)
+    (void)launch_k(latent_prep_kernel<bf16, bf16>, dim3(a.T), dim3(256), smem, st, a);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- absorbed query
+// CTA = (8 tokens, head).  The tokens' unrotated query parts sit in shared memory; thread r
+// walks the head's [dim][R] slice of W_uk (r contiguous: coalesced) and keeps 8 accumulators.
+constexpr int LQ_TT = 8;
+template <typename QT, typename WT>
+__global__ void __launch_bounds__(128) latent_q_kernel(LatentArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float qs[];  // [LQ_TT][dim + rot]
+  const int t0 = blockIdx.x * LQ_TT, hd = blockIdx.y;
+  const int dq = a.dim + a.rot, Dk = a.R + a.rot;
+  const int nt = min(LQ_TT, a.T - t0);
+  pdl_wait();
+  for (int i = threadIdx.x; i < LQ_TT * dq; i += blockDim.x) {
+    const int tt = i / dq, d = i % dq;
+    float s = 0.f;
+    if (tt < nt)
+      for (int k = 0; k < a.q_S; k++)
+        s += a.q_p[(size_t)k * a.q_stride + (size_t)(t0 + tt) * a.q_ld + hd * dq + d];
+    qs[i] = s;
+  }
+  __syncthreads();
+  QT* out = (QT*)a.qabs;
+  const WT* W = (const WT*)a.w_uk + (size_t)hd * a.dim * a.R;
+  for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
+    float acc[LQ_TT];
+#pragma unroll
+    for (int tt = 0; tt < LQ_TT; tt++) acc[tt] = 0.f;
+    for (int d = 0; d < a.dim; d++) {
+      const float w = to_f32(W[(size_t)d * a.R + r]);
+#pragma unroll
+      for (int tt = 0; tt < LQ_TT; tt++) acc[tt] = fmaf(qs[tt * dq + d], w, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LQ_TT; tt++)
+      if (tt < nt) out[((size_t)(t0 + tt) * a.H + hd) * Dk + r] = from_f32<QT>(acc[tt]);
+  }
+  const int half = a.rot_dims / 2;
+  for (int i = threadIdx.x; i < nt * a.rot; i += blockDim.x) {
+    const int tt = i / a.rot, d = i % a.rot, t = t0 + tt;
+    const float* qr = qs + tt * dq + a.dim;
+    float o = qr[d];
+    if (d < half) {
+      o = qr[d] * a.cosT[(size_t)t * half + d] - qr[d + half] * a.sinT[(size_t)t * half + d];
+    } else if (d < a.rot_dims) {
+      const int j = d - half;
+      o = qr[d] * a.cosT[(size_t)t * half + j] + qr[j] * a.sinT[(size_t)t * half + j];
+    }
+    out[((size_t)t * a.H + hd) * Dk + a.R + d] = from_f32<QT>(o);
+  }
+}
+
+cudaError_t launch_latent_q(cudaStream_t st, int qdt, int wdt, const LatentArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  dim3 grid(ceil_div(a.T, LQ_TT), a.H);
+  const size_t smem = (size_t)LQ_TT * (a.dim + a.rot) * sizeof(float);
+  if (qdt == DT_F32 && wdt == DT_F32)
+    (void)launch_k(latent_q_kernel<float, float>, grid, dim3(128), smem, st, a);
+  else if (qdt == DT_BF16 && wdt == DT_BF16)
+    (void)launch_k(latent_q_kernel<bf16, bf16>, grid, dim3(128), smem, st, a);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- attention
+// grid (tiles, item chunks, key splits).  A tile is LAT_QTILE consecutive new tokens of one
+// sequence (the host's tile list; without one, tile = sequence and its single new token).  The
+// tile's (query, head) items are dealt to warps, LAT_WARPS per CTA; all of them read the same
+// key tiles from shared memory.  Lane j scores key j of a tile (the whole Dk-long dot product,
+// query broadcast from shared memory), the warp takes max / sum, and for the weighted sum lane i
+// owns latent entries i, i + 32, ... in registers.
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float sm[];
+  const int Dk = a.R + a.rot, ldk = Dk + 1;
+  float* Ks = sm;                       // [LAT_KT][Dk + 1]
+  float* Qs = sm + LAT_KT * ldk;        // [LAT_WARPS][Dk]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+  const int tile = blockIdx.x;
+  const int seq = a.tile_seq ? a.tile_seq[tile] : tile;
+  const int q0 = a.tile_q0 ? a.tile_q0[tile] : 0;
+  const int row0 = a.cu_q[seq];
+  const int n_new = a.cu_q[seq + 1] - row0;
+  const int start = a.seq_start[seq];
+  const int nq = min(a.qtile, n_new - q0);
+  const int item0 = blockIdx.y * LAT_WARPS;
+  if (item0 >= nq * a.H) return;
+  const int item = item0 + warp;
+  const bool valid = item < nq * a.H;
+  const int qi = valid ? item / a.H : 0, head = valid ? item % a.H : 0;
+  const int row = row0 + q0 + qi;
+  const int qpos = start + q0 + qi;  // last visible key position of this item
+  // keys this CTA needs: up to its last item's position; a split takes a contiguous share
+  const int last_q = min(nq - 1, (item0 + LAT_WARPS - 1) / a.H);
+  const int kv_end = start + q0 + last_q + 1;
+  const int n_tiles_k = ceil_div(kv_end, LAT_KT);
+  const int per = ceil_div(n_tiles_k, (int)gridDim.z);
+  const int kt0 = blockIdx.z * per, kt1 = min(n_tiles_k, kt0 + per);
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const KT* pool = (const KT*)a.pool;
+
+  if (valid) {
+    const QT* qp = (const QT*)a.qabs + ((size_t)row * a.H + head) * Dk;
+    for (int d = lane; d < Dk; d += 32) Qs[warp * Dk + d] = to_f32(qp[d]) * a.scale;
+  }
+  float acc[LAT_NACC];
+#pragma unroll
+  for (int i = 0; i < LAT_NACC; i++) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const float* qv = Qs + warp * Dk;
+
+  for (int kt = kt0; kt < kt1; kt++) {
+    const int k0 = kt * LAT_KT;
+    const int nk = min(LAT_KT, kv_end - k0);
+    __syncthreads();
+    // a tile never straddles a block (LAT_KT divides KV_BLOCK)
+    const KT* src = pool + ((size_t)bt[k0 / KV_BLOCK] * KV_BLOCK + (k0 % KV_BLOCK)) * Dk;
+    for (int i = threadIdx.x; i < nk * Dk; i += blockDim.x) Ks[(i / Dk) * ldk + (i % Dk)] = to_f32(src[i]);
+    __syncthreads();
+    if (!valid) continue;
+    const int vis = min(nk, qpos - k0 + 1);  // keys of this tile the item sees
+    if (vis <= 0) continue;
+    float s = -INFINITY;
+    if (lane < vis) {
+      const float* kr = Ks + lane * ldk;
+      float d0 = 0.f, d1 = 0.f;
+      int d = 0;
+      for (; d + 1 < Dk; d += 2) {
+        d0 = fmaf(qv[d], kr[d], d0);
+        d1 = fmaf(qv[d + 1], kr[d + 1], d1);
+      }
+      if (d < Dk) d0 = fmaf(qv[d], kr[d], d0);
+      s = d0 + d1;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);  // m = -inf on the first visible tile -> 0
+    const float p = lane < vis ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < LAT_NACC; i++) acc[i] *= corr;
+    for (int j = 0; j < vis; j++) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const float* vr = Ks + j * ldk;
+#pragma unroll
+      for (int i = 0; i < LAT_NACC; i++)
+        if (i * 32 < a.R) {
+          const int r = i * 32 + lane;
+          if (r < a.R) acc[i] = fmaf(pj, vr[r], acc[i]);
+        }
+    }
+    m = m_new;
+  }
+  if (!valid) return;
+  if (gridDim.z == 1) {
+    const float inv = 1.0f / l;
+    QT* op = (QT*)a.olat + ((size_t)row * a.H + head) * a.R;
+#pragma unroll
+    for (int i = 0; i < LAT_NACC; i++) {
+      const int r = i * 32 + lane;
+      if (r < a.R) op[r] = from_f32<QT>(acc[i] * inv);
+    }
+  } else {
+    // split record: [R] unnormalised sum, then m, l
+    float* rec = a.split_ws + (((size_t)row * a.H + head) * gridDim.z + blockIdx.z) * (a.R + 2);
+#pragma unroll
+    for (int i = 0; i < LAT_NACC; i++) {
+      const int r = i * 32 + lane;
+      if (r < a.R) rec[r] = acc[i];
+    }
+    if (lane == 0) {
+      rec[a.R] = m;
+      rec[a.R + 1] = l;
+    }
+  }
+}
+
+template <typename QT>
+__global__ void latent_combine_kernel(LatentArgs a, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t item = blockIdx.x;  // row * H + head
+  const float* rec = a.split_ws + item * n_splits * (a.R + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; s++) m = fmaxf(m, rec[(size_t)s * (a.R + 2) + a.R]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; s++) {
+    const float ms = rec[(size_t)s * (a.R + 2) + a.R];
+    if (ms != -INFINITY) l += rec[(size_t)s * (a.R + 2) + a.R + 1] * expf(ms - m);
+  }
+  QT* op = (QT*)a.olat + item * a.R;
+  for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+      const float ms = rec[(size_t)s * (a.R + 2) + a.R];
+      if (ms != -INFINITY) o += rec[(size_t)s * (a.R + 2) + r] * expf(ms - m);
+    }
+    op[r] = from_f32<QT>(o / l);
+  }
+}
+
+int latent_attn_qtile() { return LAT_QTILE; }
+
+int latent_attn_splits(int n_seqs, int H, int max_len, int sm_count) {
+  const int ctas = n_seqs * ceil_div(H, LAT_WARPS);
+  int ns = ceil_div(2 * sm_count, ctas);
+  ns = min(ns, ceil_div(max_len, 8 * LAT_KT));  // at least 8 key tiles per split
+  return max(1, min(ns, 64));
+}
+
+cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a) {
+  if (a.n_tiles <= 0) return cudaSuccess;
+  if (a.R > 32 * LAT_NACC || (KV_BLOCK % LAT_KT) != 0) return cudaErrorInvalidValue;
+  const int Dk = a.R + a.rot;
+  const size_t smem = ((size_t)LAT_KT * (Dk + 1) + (size_t)LAT_WARPS * Dk) * sizeof(float);
+  const int ns = max(1, a.n_splits);
+  dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, LAT_WARPS), ns);
+  if (qdt == DT_F32 && kvdt == DT_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(latent_attn_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(latent_attn_kernel<float, float>, grid, dim3(LAT_WARPS * 32), smem, st, a);
+    if (ns > 1) (void)launch_k(latent_combine_kernel<float>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+  } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(latent_attn_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(latent_attn_kernel<bf16, bf16>, grid, dim3(LAT_WARPS * 32), smem, st, a);
+    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- value expansion + head gate
+// out[t, h * vdim + e] = gate[t, h] * sum_r o[t, h, r] * W_uv[h * vdim + e, r]
+constexpr int LO_TT = 8;
+template <typename QT, typename WT>
+__global__ void __launch_bounds__(128) latent_out_kernel(LatentArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float os[];  // [LO_TT][R]
+  const int t0 = blockIdx.x * LO_TT, hd = blockIdx.y;
+  const int nt = min(LO_TT, a.T - t0);
+  pdl_wait();
+  const QT* o = (const QT*)a.olat;
+  for (int i = threadIdx.x; i < LO_TT * a.R; i += blockDim.x) {
+    const int tt = i / a.R, r = i % a.R;
+    os[i] = tt < nt ? to_f32(o[((size_t)(t0 + tt) * a.H + hd) * a.R + r]) : 0.f;
+  }
+  __syncthreads();
+  QT* out = (QT*)a.attn_out;
+  const WT* W = (const WT*)a.w_uv + (size_t)hd * a.vdim * a.R;
+  for (int e = threadIdx.x; e < a.vdim; e += blockDim.x) {
+    float acc[LO_TT];
+#pragma unroll
+    for (int tt = 0; tt < LO_TT; tt++) acc[tt] = 0.f;
+    const WT* wr = W + (size_t)e * a.R;
+    for (int r = 0; r < a.R; r++) {
+      const float w = to_f32(wr[r]);
+#pragma unroll
+      for (int tt = 0; tt < LO_TT; tt++) acc[tt] = fmaf(os[tt * a.R + r], w, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LO_TT; tt++)
+      if (tt < nt)
+        out[(size_t)(t0 + tt) * a.ov_p + hd * a.vdim + e] =
+            from_f32<QT>(acc[tt] * a.gate[(size_t)(t0 + tt) * a.H + hd]);
+  }
+  // zero the padding columns of the O projection's input once per token tile
+  if (hd == 0)
+    for (int i = threadIdx.x; i < nt * (a.ov_p - a.H * a.vdim); i += blockDim.x) {
+      const int pad = a.ov_p - a.H * a.vdim;
+      out[(size_t)(t0 + i / pad) * a.ov_p + a.H * a.vdim + i % pad] = from_f32<QT>(0.f);
+    }
+}
+
+cudaError_t launch_latent_out(cudaStream_t st, int qdt, int wdt, const LatentArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  dim3 grid(ceil_div(a.T, LO_TT), a.H);
+  const size_t smem = (size_t)LO_TT * a.R * sizeof(float);
+  if (qdt == DT_F32 && wdt == DT_F32)
+    (void)launch_k(latent_out_kernel<float, float>, grid, dim3(128), smem, st, a);
+  else if (qdt == DT_BF16 && wdt == DT_BF16)
+    (void)launch_k(latent_out_kernel<bf16, bf16>, grid, dim3(128), smem, st, a);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// logits <- cap * tanh(logits / cap), summing S split-K slices on the way
+__global__ void softcap_kernel(const float* __restrict__ p, int S, size_t stride, size_t n, float cap,
+                               float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < S; k++) s += p[(size_t)k * stride + i];
+    out[i] = cap > 0.f ? cap * tanhf(s / cap) : s;
+  }
+}
+cudaError_t launch_softcap(cudaStream_t st, const float* p, int S, size_t stride, size_t n, float cap,
+                           float* out) {
+  if (n == 0) return cudaSuccess;
+  const int blocks = (int)min((size_t)148 * 8, (n + 255) / 256);
+  (void)launch_k(softcap_kernel, dim3(blocks), dim3(256), 0, st, p, S, stride, n, cap, out);
+  return cudaGetLastError();
+}
+
+}  // namespace nvllm

@@ -91,6 +91,17 @@ __device__ __forceinline__ float silu(float x) {  // mamba2.go:360-367
   return x / (1.0f + expf(-x));
 }
 
+// gated unit of a GLU feed-forward: limit <= 0: silu(g) * u; limit > 0: the clamped form
+// min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1)
+__device__ __forceinline__ float glu_unit(float g, float u, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return silu(g) * u;
+}
+
 // ---- reductions -------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
   const int r = a.row_idx ? a.row_idx[orow] - a.row_bias : orow;
   float* xr = a.x + (size_t)r * H;
   const bool upd = (a.p1 != nullptr) || (a.p2 != nullptr);
+  const bool ln = a.b != nullptr || a.centered != 0;  // LayerNorm (with or without the additive term)
   float lsum = 0.f;
   for (int i = i0; i < H; i += blockDim.x * 8) {
     float v[8];
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
     }
     if (upd) store8(xr + i, v);
     store8(row + i, v);
-    if (a.b) {
+    if (ln) {
 #pragma unroll
       for (int j = 0; j < 8; j++) lsum += v[j];
     } else {
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
   float tot = block_sum(lsum, red);
   const unsigned long long t_red = tr.buf ? gtime() : 0ull;
   float mean = 0.f, inv;
-  if (a.b) {
+  if (ln) {
     mean = tot / (float)H;
     float lv = 0.f;
     for (int i = i0; i < H; i += blockDim.x * 8) {
@@ -222,8 +223,11 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 #pragma unroll
         for (int j = 0; j < 8; j++) w[j] = 1.f;
       if (a.b) load8(a.b + i, bb);
+      else
+#pragma unroll
+        for (int j = 0; j < 8; j++) bb[j] = 0.f;
     }
-    if (a.b) {
+    if (ln) {
 #pragma unroll
       for (int j = 0; j < 8; j++) o[j] = (row[i + j] - mean) * inv * w[j] + bb[j];
     } else {
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
   if (a.router) {
     __shared__ float probs[MOE_MAX_E];
     __syncthreads();
-    moe_route_row(row, a.router, H, a.E, a.topk, probs, (size_t)orow, a.topk_idx, a.topk_w);
+    moe_route_row(row, a.router, H, a.E, a.topk, probs, (size_t)orow, a.topk_idx, a.topk_w, a.route);
   }
   if (threadIdx.x == 0 && trace_on(tr))
     trace_rec(tr, t_entry, t_wait, ((t_loads - t_wait) << 32) | (t_red - t_wait));
@@ -261,7 +265,8 @@ cudaError_t launch_norm(cudaStream_t st, const NormArgs& a) {
 // ---------------------------------------------------------------- activations
 template <typename OT>
 __global__ void act_kernel(int T, int F, const float* __restrict__ h, int S, size_t stride,
-                           const float* __restrict__ bias, int swiglu, OT* __restrict__ out, Trace tr) {
+                           const float* __restrict__ bias, int swiglu, OT* __restrict__ out, float glu_limit,
+                           Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
@@ -298,8 +303,8 @@ __global__ void act_kernel(int T, int F, const float* __restrict__ h, int S, siz
       }
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        o[i] = silu(a[2 * i]) * a[2 * i + 1];
-        o[4 + i] = silu(b[2 * i]) * b[2 * i + 1];
+        o[i] = glu_unit(a[2 * i], a[2 * i + 1], glu_limit);
+        o[4 + i] = glu_unit(b[2 * i], b[2 * i + 1], glu_limit);
       }
     } else {
       if (bias) {
@@ -317,15 +322,15 @@ __global__ void act_kernel(int T, int F, const float* __restrict__ h, int S, siz
 }
 
 cudaError_t launch_act(cudaStream_t st, int odt, int T, int F, const float* h, int S, size_t stride,
-                       const float* bias, int swiglu, void* out) {
+                       const float* bias, int swiglu, void* out, float glu_limit) {
   if (T <= 0) return cudaSuccess;
   size_t nvec = (size_t)T * (F / 8);
   int threads = 256;
   int blocks = (int)min((size_t)148 * 16, (nvec + threads - 1) / threads);
   if (odt == DT_F32)
-    (void)launch_k(act_kernel<float>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (float*)out, next_trace(6));
+    (void)launch_k(act_kernel<float>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (float*)out, glu_limit, next_trace(6));
   else
-    (void)launch_k(act_kernel<bf16>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (bf16*)out, next_trace(6));
+    (void)launch_k(act_kernel<bf16>, dim3(blocks), dim3(threads), 0, st, T, F, h, S, stride, bias, swiglu, (bf16*)out, glu_limit, next_trace(6));
   return cudaGetLastError();
 }
 

@@ -1,0 +1,501 @@
+// forward_layered.cu — models whose configuration lists their layers one by one
+// (nvllm_create_layered): handle set-up, tensors by checkpoint name, the cache pools and the
+// forward pass of one engine step.
+//
+// Every layer is a parallel block on the fp32 residual stream x:
+//     h = LayerNorm(x) (weight only);  x += mixer(h) + feed_forward(h)
+// Mixer "latent attention" (attention_latent.cu): one fused input projection [W_dq | W_dkv | W_g]
+// of h, RMS-normed latents, a query up projection, the absorbed-query attention over the paged
+// latent cache, value expansion + per-head sigmoid gate, output projection.  A layer with
+// kv_from = j has no W_dkv and reads layer j's cache rows (written earlier in the same step).
+// Feed-forward: none, a dense clamped gated unit, or a group-limited top-k mixture of such
+// units (the routing runs inside the norm kernel, the expert GEMMs are the grouped ones the
+// other MoE models use).  The two sublayer results stay pending as split-K partials and are
+// added to x by the next layer's norm kernel, as everywhere in this library.
+#include <math.h>
+
+#include <string>
+
+#include "forward_ops.h"
+
+namespace nvllm {
+
+static size_t up8(size_t a) { return (a + 7) / 8 * 8; }
+static size_t wire_size(int api_dt) { return api_dt == NVLLM_DT_F32 ? 4 : 2; }
+
+void layered_free(nvllm_handle* h) {
+  auto F = [](void* p) {
+    if (p) cudaFree(p);
+  };
+  for (auto& y : h->ll) {
+    F(y.norm_w); F(y.w_in); F(y.dq_norm); F(y.dkv_norm); F(y.w_uq); F(y.w_uk); F(y.w_uv); F(y.w_o);
+    F(y.w1); F(y.w2); F(y.router); F(y.moe_in); F(y.moe_out);
+  }
+  h->ll.clear();
+  for (void* p : h->lat_pools) F(p);
+  h->lat_pools.clear();
+  for (auto& r : h->ropes) {
+    F(r.inv_freq); F(r.cosT); F(r.sinT);
+  }
+  h->ropes.clear();
+}
+
+// ------------------------------------------------------------------ tensors by name
+namespace {
+struct Dst {
+  void* p = nullptr;     // destination base
+  int ddt = DT_F32;      // destination dtype
+  int64_t rows = 0, cols = 0;  // expected shape ([rows] when cols == 0)
+  int ld = 0;            // destination row stride (elements)
+  int row_mul = 1, row_add = 0;
+};
+}  // namespace
+
+static bool parse_layer_name(const std::string& name, int* layer, std::string* rest) {
+  if (name.size() < 3 || name[0] != 'l' || name[1] < '0' || name[1] > '9') return false;
+  size_t i = 1;
+  int v = 0;
+  while (i < name.size() && name[i] >= '0' && name[i] <= '9') v = v * 10 + (name[i++] - '0');
+  if (i >= name.size() || name[i] != '.') return false;
+  *layer = v;
+  *rest = name.substr(i + 1);
+  return true;
+}
+
+int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void* host,
+                       const int64_t* shape, int ndim) {
+  if (!h->layered) return set_err(h, NVLLM_ERR_STATE, "named weights belong to handles of nvllm_create_layered");
+  if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "set_named_weight after finalize");
+  if (!cname || !host || !shape || ndim < 1 || ndim > 2) return set_err(h, NVLLM_ERR_INVALID, "bad named weight");
+  if (dtype < 0 || dtype > 2) return set_err(h, NVLLM_ERR_INVALID, "bad dtype %d", dtype);
+  NV_CHECK(h, cudaSetDevice(h->dev));
+  const std::string name(cname);
+  const int W = h->H, wdt = h->wdt;
+  const size_t wsz = dt_size(wdt);
+  Dst d;
+  auto vec = [&](float* p, int64_t n) { d.p = p; d.ddt = DT_F32; d.rows = n; d.cols = 0; };
+  auto mat = [&](void* p, int64_t rows, int64_t cols, int ld, size_t row0 = 0, int mul = 1, int add = 0) {
+    d.p = (char*)p + row0 * (size_t)ld * wsz; d.ddt = wdt; d.rows = rows; d.cols = cols; d.ld = ld;
+    d.row_mul = mul; d.row_add = add;
+  };
+  int l = -1;
+  std::string rest;
+  if (name == "embed") mat(h->wte, h->V, W, W);
+  else if (name == "head") mat(h->lm_head, h->V, W, W);
+  else if (name == "final.norm") vec(h->lnf_w, W);
+  else if (parse_layer_name(name, &l, &rest) && l < h->L) {
+    ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    const int own = s.kv_from < 0;
+    if (rest == "norm1") vec(y.norm_w, W);
+    else if (rest == "mix.dq") mat(y.w_in, s.q_rank, W, W, 0);
+    else if (rest == "mix.dkv" && own) mat(y.w_in, y.Dk, W, W, s.q_rank);
+    else if (rest == "mix.g") mat(y.w_in, s.heads, W, W, s.q_rank + (own ? y.Dk : 0));
+    else if (rest == "mix.dq.norm") vec(y.dq_norm, s.q_rank);
+    else if (rest == "mix.dkv.norm" && own) vec(y.dkv_norm, s.kv_rank);
+    else if (rest == "mix.uq") mat(y.w_uq, y.q_cols, s.q_rank, y.q_rank_p);
+    else if (rest == "mix.uk") mat(y.w_uk, (int64_t)s.heads * s.dim, s.kv_rank, s.kv_rank);
+    else if (rest == "mix.uv") mat(y.w_uv, (int64_t)s.heads * s.vdim, s.kv_rank, s.kv_rank);
+    else if (rest == "mix.o") mat(y.w_o, W, (int64_t)s.heads * s.vdim, y.ov_p);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.gate") mat(y.w1, s.ff, W, W, 0, 2, 0);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.up") mat(y.w1, s.ff, W, W, 0, 2, 1);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.down") mat(y.w2, W, s.ff, s.ff);
+    else if (s.mlp == NVLLM_MLP_MOE && rest == "mlp.router") {
+      mat(y.router, s.experts, W, W);
+      d.ddt = DT_F32;
+      d.p = y.router;
+    } else if (s.mlp == NVLLM_MLP_MOE && rest.compare(0, 5, "mlp.e") == 0) {
+      size_t i = 5;
+      int e = 0;
+      while (i < rest.size() && rest[i] >= '0' && rest[i] <= '9') e = e * 10 + (rest[i++] - '0');
+      const std::string part = i < rest.size() ? rest.substr(i) : "";
+      if (i == 5 || e >= s.experts) return set_err(h, NVLLM_ERR_INVALID, "unknown tensor %s", cname);
+      if (part == ".gate") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * s.ff, 2, 0);
+      else if (part == ".up") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * s.ff, 2, 1);
+      else if (part == ".down") mat(y.moe_out, W, s.ff, s.ff, (size_t)e * W);
+    }
+  }
+  if (!d.p) return set_err(h, NVLLM_ERR_INVALID, "tensor %s does not belong to this model", cname);
+  const bool is_vec = d.cols == 0;
+  if ((is_vec && (ndim != 1 || shape[0] != d.rows)) ||
+      (!is_vec && (ndim != 2 || shape[0] != d.rows || shape[1] != d.cols)))
+    return set_err(h, NVLLM_ERR_INVALID, "tensor %s: shape [%lld%s%lld] where [%lld%s%lld] is expected", cname,
+                   (long long)shape[0], ndim > 1 ? ", " : "", ndim > 1 ? (long long)shape[1] : 0LL,
+                   (long long)d.rows, is_vec ? "" : ", ", (long long)d.cols);
+  const size_t numel = (size_t)d.rows * (is_vec ? 1 : d.cols);
+  void* stage = nullptr;
+  NV_CHECK(h, cudaMalloc(&stage, numel * wire_size(dtype)));
+  cudaError_t e = cudaMemcpyAsync(stage, host, numel * wire_size(dtype), cudaMemcpyHostToDevice, h->stream);
+  if (e == cudaSuccess) {
+    if (is_vec) e = launch_convert(h->stream, dtype, stage, numel, DT_F32, d.p);
+    else e = launch_copy_rows(h->stream, dtype, stage, (size_t)d.cols, (int)d.rows, (int)d.cols, d.ddt, d.p,
+                              d.ld, d.row_mul, d.row_add);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  cudaFree(stage);
+  if (e != cudaSuccess) return set_err(h, NVLLM_ERR_CUDA, "tensor %s: %s", cname, cudaGetErrorString(e));
+  h->named_got.push_back(name);
+  return NVLLM_OK;
+}
+
+int layered_finalize(nvllm_handle* h) {
+  auto got = [&](const std::string& n) {
+    for (auto& g : h->named_got)
+      if (g == n) return true;
+    return false;
+  };
+  std::vector<std::string> need = {"embed", "head", "final.norm"};
+  for (int l = 0; l < h->L; l++) {
+    const nvllm_layer_spec& s = h->ll[l].s;
+    const std::string p = "l" + std::to_string(l) + ".";
+    for (const char* n : {"norm1", "mix.dq", "mix.dq.norm", "mix.uq", "mix.uk", "mix.uv", "mix.g", "mix.o"})
+      need.push_back(p + n);
+    if (s.kv_from < 0) {
+      need.push_back(p + "mix.dkv");
+      need.push_back(p + "mix.dkv.norm");
+    }
+    if (s.mlp == NVLLM_MLP_DENSE)
+      for (const char* n : {"mlp.gate", "mlp.up", "mlp.down"}) need.push_back(p + n);
+    if (s.mlp == NVLLM_MLP_MOE) {
+      need.push_back(p + "mlp.router");
+      for (int e = 0; e < s.experts; e++)
+        for (const char* n : {".gate", ".up", ".down"}) need.push_back(p + "mlp.e" + std::to_string(e) + n);
+    }
+  }
+  for (auto& n : need)
+    if (!got(n)) return set_err(h, NVLLM_ERR_INVALID, "missing tensor %s", n.c_str());
+  // cache pools: one per layer with its own down projection, rows [c | rotated key part]
+  h->lat_pools.assign(h->L, nullptr);
+  for (int l = 0; l < h->L; l++) {
+    ListedLayer& y = h->ll[l];
+    if (y.s.kv_from >= 0) continue;
+    const size_t bytes = (size_t)h->num_blocks * KV_BLOCK * y.Dk * dt_size(h->kvdt);
+    cudaError_t e = cudaMalloc(&h->lat_pools[l], bytes);
+    if (e != cudaSuccess)
+      return set_err(h, NVLLM_ERR_NOMEM, "latent cache of %d blocks does not fit: %s", h->num_blocks,
+                     cudaGetErrorString(e));
+    NV_CHECK(h, cudaMemsetAsync(h->lat_pools[l], 0, bytes, h->stream));
+    h->kv_bytes += bytes;
+  }
+  // rotation frequencies base^(-2i/dims), in double
+  for (auto& r : h->ropes) {
+    const int half = r.dims / 2;
+    std::vector<double> f(half);
+    for (int i = 0; i < half; i++) f[i] = pow(r.base, -2.0 * (double)i / (double)r.dims);
+    NV_CHECK(h, cudaMalloc((void**)&r.inv_freq, (size_t)half * 8));
+    NV_CHECK(h, cudaMemcpy(r.inv_freq, f.data(), (size_t)half * 8, cudaMemcpyHostToDevice));
+  }
+  NV_CHECK(h, cudaStreamSynchronize(h->stream));
+  h->finalized = true;
+  return NVLLM_OK;
+}
+
+// ------------------------------------------------------------------ forward pass
+int forward_step_layered(nvllm_handle* h) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const int T = L.T, n = L.n, n_out = L.n_out > 0 ? L.n_out : L.n, H = h->H;
+  const int32_t* d = L.d;
+  const int* d_pos = d + L.positions;
+  cudaStream_t st = h->stream;
+  const double asz = dt_size(h->adt), kvsz = dt_size(h->kvdt), wsz = dt_size(h->wdt);
+  int rc;
+  {
+    ProfScope ps(h, NVLLM_K_EMBED, (double)T * H * (4 + wsz), 0);
+    LAUNCH(h, launch_embed(st, h->wdt, d + L.tokens, d_pos, h->wte, nullptr, 0, h->cfg.embedding_multiplier,
+                           w.x, T, H));
+  }
+  for (auto& r : h->ropes) {
+    ProfScope ps(h, NVLLM_K_MISC, (double)T * r.dims * 4, 0);
+    LAUNCH(h, launch_rope_table(st, d_pos, T, r.dims / 2, r.inv_freq, r.cosT, r.sinT));
+  }
+  Pending p1, p2;
+  for (int l = 0; l < h->L; l++) {
+    const ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    RouterArgs ra;
+    if (s.mlp == NVLLM_MLP_MOE) {
+      ra.R = y.router; ra.E = s.experts; ra.k = s.top;
+      ra.topk_idx = w.topk_idx; ra.topk_w = w.topk_w;
+      ra.opts = RouteOpts{s.groups, s.keep_groups, 1, s.router_scale};
+    }
+    if ((rc = run_norm(h, w.x, &p1, &p2, y.norm_w, nullptr, w.xn, nullptr, nullptr, T,
+                       s.mlp == NVLLM_MLP_MOE ? &ra : nullptr, true)))
+      return rc;
+    // ---- mixer: latent attention
+    const int own = s.kv_from < 0;
+    Pending pin;
+    if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+    const RopeTable& rt = h->ropes[y.rope];
+    LatentArgs a{};
+    a.T = T; a.H = s.heads; a.dim = s.dim; a.rot = s.rot_dim; a.rot_dims = s.rot_dims; a.vdim = s.vdim;
+    a.R = s.kv_rank; a.q_rank = s.q_rank; a.q_rank_p = y.q_rank_p; a.ov_p = y.ov_p; a.own_kv = own;
+    a.eps = h->cfg.norm_eps; a.scale = s.scale;
+    a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
+    a.dq_norm = y.dq_norm; a.dkv_norm = y.dkv_norm;
+    a.cosT = rt.cosT; a.sinT = rt.sinT;
+    a.slots = d + L.slots;
+    a.pool = h->lat_pools[y.pool];
+    a.cq = w.lat_cq; a.gate = w.lat_gate;
+    a.w_uk = y.w_uk; a.qabs = w.q;
+    a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
+    a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start;
+    a.olat = w.lat_o; a.w_uv = y.w_uv; a.attn_out = w.attn_out;
+    a.split_ws = w.attn_ws;
+    if (L.prefill) {
+      a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles;
+      a.qtile = LAT_QTILE; a.n_splits = 1;
+    } else {
+      a.n_tiles = n; a.qtile = 1;
+      a.n_splits = latent_attn_splits(n, s.heads, L.max_len, h->sm_count);
+      while (a.n_splits > 1 && (size_t)T * s.heads * a.n_splits * (s.kv_rank + 2) > w.attn_ws_floats) a.n_splits--;
+    }
+    {
+      ProfScope ps(h, NVLLM_K_ROPE_KV, (double)T * y.n_in * 4 + (double)T * (y.q_rank_p * asz + own * y.Dk * kvsz), 0,
+                   (double)T * y.n_in * 4 * (pin.S - 1));
+      LAUNCH(h, launch_latent_prep(st, h->adt, h->kvdt, a));
+    }
+    Pending pq;
+    if ((rc = run_gemm(h, w.lat_cq, y.q_rank_p, y.w_uq, T, y.q_cols, y.q_rank_p, 1.f, w.ws_a, w.ws_a_floats,
+                       y.q_cols, &pq)))
+      return rc;
+    a.q_p = pq.p; a.q_S = pq.S; a.q_stride = pq.stride; a.q_ld = y.q_cols;
+    {
+      ProfScope ps(h, NVLLM_K_ROPE_KV, (double)T * y.q_cols * 4 + (double)T * s.heads * y.Dk * asz +
+                                           (double)s.heads * s.dim * s.kv_rank * wsz,
+                   2.0 * T * s.heads * s.dim * s.kv_rank, (double)T * y.q_cols * 4 * (pq.S - 1));
+      LAUNCH(h, launch_latent_q(st, h->adt, h->wdt, a));
+    }
+    {
+      // algorithmic: every cached row of the contexts once; flops: scores over Dk, sums over R
+      const double bytes = (double)L.sum_len * y.Dk * kvsz;
+      const double flops = 2.0 * s.heads * (y.Dk + s.kv_rank) * L.attn_pairs;
+      ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE, bytes, flops,
+                   (double)T * s.heads * (y.Dk + s.kv_rank) * asz);
+      LAUNCH(h, launch_latent_attn(st, h->adt, h->kvdt, a));
+      if (a.n_splits > 1) h->launches++;
+    }
+    {
+      ProfScope ps(h, NVLLM_K_MISC, (double)T * (s.heads * s.kv_rank + y.ov_p) * asz +
+                                        (double)s.heads * s.vdim * s.kv_rank * wsz,
+                   2.0 * T * s.heads * s.vdim * s.kv_rank);
+      LAUNCH(h, launch_latent_out(st, h->adt, h->wdt, a));
+    }
+    Pending pa;
+    if ((rc = run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, &pa))) return rc;
+    // ---- feed-forward on the same normed input
+    Pending pm;
+    if (s.mlp == NVLLM_MLP_DENSE) {
+      Pending h1;
+      h->glu_limit_cur = s.limit;
+      rc = run_gemm(h, w.xn, H, y.w1, T, 2 * s.ff, H, 1.f, w.ws_a, w.ws_a_floats, 2 * s.ff, &h1, TC5_EPI_SWIGLU,
+                    w.hbuf, s.ff, nullptr);
+      h->glu_limit_cur = 0.f;
+      if (rc) return rc;
+      if (h1.S > 0) {
+        ProfScope ps(h, NVLLM_K_ACT, (double)T * 2 * s.ff * 4 + (double)T * s.ff * asz, 0,
+                     (double)T * 2 * s.ff * 4 * (h1.S - 1));
+        LAUNCH(h, launch_act(st, h->adt, T, s.ff, h1.p, h1.S, h1.stride, nullptr, 1, w.hbuf, s.limit));
+      }
+      if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
+    } else if (s.mlp == NVLLM_MLP_MOE) {
+      if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, s.ff, s.limit, y.moe_in, y.moe_out, &pm))) return rc;
+    }
+    if (pm.p) {
+      p1 = pm;  // the expert combine can only be the first addend of the norm kernel
+      p2 = pa;
+    } else {
+      p1 = pa;
+      p2 = Pending();
+    }
+  }
+  // final norm + LM head on the rows that were asked for: each sequence's last, then the extra ones
+  if ((rc = run_norm(h, w.x, &p1, &p2, h->lnf_w, nullptr, w.xn_last, nullptr, d + L.last_row, n_out, nullptr, true)))
+    return rc;
+  Pending lg;
+  if ((rc = run_gemm(h, w.xn_last, H, h->lm_head, n_out, h->V, H, 1.f, w.logits_p, w.logits_p_floats, h->ldl, &lg, 0,
+                     nullptr, 0, nullptr, nullptr, 0, (double)n_out * h->V * 4)))
+    return rc;
+  {
+    ProfScope ps(h, NVLLM_K_MISC, (double)n_out * h->ldl * 8, 0, (double)n_out * h->ldl * 4 * (lg.S - 1));
+    LAUNCH(h, launch_softcap(st, lg.p, lg.S, lg.stride, (size_t)n_out * h->ldl, h->logit_softcap, w.logits));
+  }
+  const float* d_temp = reinterpret_cast<const float*>(d + L.temperature);
+  const float* d_uni = reinterpret_cast<const float*>(d + L.uniforms);
+  {
+    ProfScope ps(h, NVLLM_K_SAMPLE, (double)n * h->V * 4, 0);
+    LAUNCH(h, launch_sample(st, w.logits, h->ldl, h->V, n, d_temp, d_uni, w.out_tokens, w.amax, w.amax_ticket, 0));
+    if (h->filters_active() && h->hist_n == n)
+      LAUNCH(h, launch_sample_filtered(st, w.logits, h->ldl, h->V, n, 0, d_temp, d_uni, h->d_hist + (n + 1),
+                                       h->d_hist, h->top_p, h->top_k, h->rep_penalty, h->d_probs, w.out_tokens));
+  }
+  h->ws.logits_final = w.logits;
+  return NVLLM_OK;
+}
+
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_layer_spec* layers,
+                                    nvllm_handle** out) {
+  if (!c || !layers || !out) return set_err(nullptr, NVLLM_ERR_INVALID, "null argument");
+  *out = nullptr;
+  if (c->abi_version != NVLLM_ABI_VERSION)
+    return set_err(nullptr, NVLLM_ERR_INVALID, "abi_version %d != %d", c->abi_version, NVLLM_ABI_VERSION);
+  auto bad = [&](int l, const char* what) {
+    return set_err(nullptr, NVLLM_ERR_INVALID, "invalid config (layer %d): %s", l, what);
+  };
+  if (c->vocab_size <= 0 || c->hidden <= 0 || c->num_layers <= 0) return bad(-1, "non-positive dimension");
+  if (c->hidden % 8) return bad(-1, "width must be a multiple of 8");
+  if (c->precision != NVLLM_PREC_FP32 && c->precision != NVLLM_PREC_BF16) return bad(-1, "precision");
+  for (int l = 0; l < c->num_layers; l++) {
+    const nvllm_layer_spec& s = layers[l];
+    if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) return bad(l, "unknown mixer kind");
+    if (s.heads <= 0 || s.dim <= 0 || s.rot_dim <= 0 || s.vdim <= 0 || s.kv_rank <= 0 || s.q_rank <= 0)
+      return bad(l, "non-positive mixer size");
+    if (s.kv_rank > 512) return bad(l, "kv_rank above 512");
+    if (s.rot_dims < 2 || s.rot_dims > s.rot_dim || (s.rot_dims & 1)) return bad(l, "rotated entries must be even and <= rot_dim");
+    if (s.kv_from >= 0) {
+      if (s.kv_from >= l) return bad(l, "kv_from must name an earlier layer");
+      const nvllm_layer_spec& j = layers[s.kv_from];
+      if (j.kv_from >= 0) return bad(l, "kv_from must name a layer with its own down projection");
+      if (j.kv_rank != s.kv_rank || j.rot_dim != s.rot_dim) return bad(l, "kv_from layer has other cache sizes");
+    }
+    if (s.mlp < NVLLM_MLP_NONE || s.mlp > NVLLM_MLP_MOE) return bad(l, "unknown feed-forward kind");
+    if (s.mlp != NVLLM_MLP_NONE && (s.ff <= 0 || s.ff % 8)) return bad(l, "ff must be a positive multiple of 8");
+    if (s.mlp != NVLLM_MLP_NONE && !(s.limit > 0.f)) return bad(l, "limit must be positive");
+    if (s.mlp == NVLLM_MLP_MOE) {
+      if (s.experts <= 0 || s.experts > 256 || s.top <= 0 || s.top > 32 || s.top > s.experts)
+        return bad(l, "experts 1..256, top 1..32");
+      const int g = s.groups > 0 ? s.groups : 1, keep = s.groups > 0 ? s.keep_groups : 1;
+      if (s.experts % g || keep <= 0 || keep > g || keep * (s.experts / g) < s.top)
+        return bad(l, "expert groups must divide the experts and the kept groups must hold `top` experts");
+    }
+  }
+  cudaError_t e = cudaSetDevice(c->device);
+  if (e != cudaSuccess)
+    return set_err(nullptr, NVLLM_ERR_CUDA, "cudaSetDevice(%d): %s (no CPU fallback exists)", c->device,
+                   cudaGetErrorString(e));
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, c->device);
+  if (e != cudaSuccess) return set_err(nullptr, NVLLM_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return set_err(nullptr, NVLLM_ERR_CUDA, "device %d is sm_%d%d; this library contains sm_100a code only",
+                   c->device, prop.major, prop.minor);
+  if (const char* env = getenv("NVLLM_PDL")) set_pdl_enabled(atoi(env) != 0);
+  nvllm_handle* h = new nvllm_handle();
+  h->layered = true;
+  nvllm_config& g = h->cfg;  // what nvllm_get_config reports; the uniform fields describe layer 0
+  g.abi_version = NVLLM_ABI_VERSION;
+  g.vocab_size = c->vocab_size; g.hidden = c->hidden; g.num_layers = c->num_layers;
+  g.num_heads = layers[0].heads; g.num_kv_heads = 1; g.head_dim = layers[0].dim + layers[0].rot_dim;
+  g.max_seq_len = 1 << 30;
+  g.attention_type = NVLLM_ATTN_MQA; g.norm_type = NVLLM_NORM_LAYER; g.position_type = NVLLM_POS_ROPE;
+  g.activation_type = NVLLM_ACT_SWIGLU; g.block_style = NVLLM_BLOCK_PARALLEL;
+  g.norm_eps = c->norm_eps; g.embedding_multiplier = c->embedding_scale;
+  g.precision = c->precision;
+  g.num_kv_blocks = c->num_kv_blocks > 0 ? c->num_kv_blocks : 1024;
+  g.max_num_seqs = c->max_num_seqs > 0 ? c->max_num_seqs : 512;
+  g.max_batched_tokens = c->max_batched_tokens > 0 ? c->max_batched_tokens : 16384;
+  g.tp_size = 1; g.device = c->device;
+  h->dev = c->device;
+  h->sm_count = prop.multiProcessorCount;
+  h->wdt = h->adt = h->kvdt = (c->precision == NVLLM_PREC_BF16) ? DT_BF16 : DT_F32;
+  h->H = c->hidden; h->V = c->vocab_size; h->L = c->num_layers;
+  h->ldl = (int)up8(h->V); h->Vl = h->ldl; h->Vl_valid = h->V;
+  h->parallel = true;
+  h->num_blocks = g.num_kv_blocks;
+  h->logit_softcap = c->logit_softcap;
+  h->graphs_enabled = 0;  // step graphs and the speculative step are keyed on the uniform models' shapes
+  h->spec_enabled = 0;
+  if (const char* env = getenv("NVLLM_SKIP")) h->skip_mask = (unsigned)strtoul(env, nullptr, 0);
+  auto fail = [&](cudaError_t ce, const char* what) {
+    int code = (ce == cudaErrorMemoryAllocation) ? NVLLM_ERR_NOMEM : NVLLM_ERR_CUDA;
+    set_err(nullptr, code, "%s: %s", what, cudaGetErrorString(ce));
+    nvllm_destroy(h);
+    return code;
+  };
+  if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail(e, "cudaStreamCreate");
+  if ((e = cudaEventCreate(&h->ev0)) != cudaSuccess) return fail(e, "cudaEventCreate");
+  if ((e = cudaEventCreate(&h->ev1)) != cudaSuccess) return fail(e, "cudaEventCreate");
+  const int W = h->H;
+  const size_t wsz = dt_size(h->wdt);
+  // zero-filled: inner extents are padded to 8 and the padding must stay zero
+  auto alloc = [&](void** p, size_t bytes) -> cudaError_t {
+    bytes = (bytes + 255) / 256 * 256;
+    cudaError_t ce = cudaMalloc(p, bytes);
+    if (ce == cudaSuccess) ce = cudaMemsetAsync(*p, 0, bytes, h->stream);
+    if (ce == cudaSuccess) h->weight_bytes += bytes;
+    return ce;
+  };
+#define AL(ptr, bytes) \
+  if ((e = alloc((void**)&(ptr), (size_t)(bytes))) != cudaSuccess) return fail(e, "cudaMalloc(weights)");
+  AL(h->wte, (size_t)h->V * W * wsz);
+  AL(h->lm_head, (size_t)h->V * W * wsz);
+  h->lm_head_owned = true;
+  AL(h->lnf_w, (size_t)W * 4);
+  h->ll.resize(h->L);
+  int qkv_cols = 0, q_cols = 0;
+  for (int l = 0; l < h->L; l++) {
+    ListedLayer& y = h->ll[l];
+    y.s = layers[l];
+    const nvllm_layer_spec& s = y.s;
+    y.Dk = s.kv_rank + s.rot_dim;
+    y.n_in = s.q_rank + (s.kv_from < 0 ? y.Dk : 0) + s.heads;
+    y.q_cols = s.heads * (s.dim + s.rot_dim);
+    y.q_rank_p = (int)up8(s.q_rank);
+    y.ov_p = (int)up8((size_t)s.heads * s.vdim);
+    y.pool = s.kv_from < 0 ? l : s.kv_from;
+    for (size_t r = 0; r < h->ropes.size(); r++)
+      if (h->ropes[r].base == (double)s.rot_base && h->ropes[r].dims == s.rot_dims) y.rope = (int)r;
+    if (y.rope < 0) {
+      RopeTable rt;
+      rt.base = s.rot_base;
+      rt.dims = s.rot_dims;
+      y.rope = (int)h->ropes.size();
+      h->ropes.push_back(rt);
+    }
+    AL(y.norm_w, (size_t)W * 4);
+    AL(y.w_in, (size_t)y.n_in * W * wsz);
+    AL(y.dq_norm, (size_t)s.q_rank * 4);
+    if (s.kv_from < 0) AL(y.dkv_norm, (size_t)s.kv_rank * 4);
+    AL(y.w_uq, (size_t)y.q_cols * y.q_rank_p * wsz);
+    AL(y.w_uk, (size_t)s.heads * s.dim * s.kv_rank * wsz);
+    AL(y.w_uv, (size_t)s.heads * s.vdim * s.kv_rank * wsz);
+    AL(y.w_o, (size_t)W * y.ov_p * wsz);
+    if (s.mlp == NVLLM_MLP_DENSE) {
+      AL(y.w1, (size_t)2 * s.ff * W * wsz);
+      AL(y.w2, (size_t)W * s.ff * wsz);
+      qkv_cols = std::max(qkv_cols, 2 * s.ff);
+      h->F = std::max(h->F, s.ff);
+    } else if (s.mlp == NVLLM_MLP_MOE) {
+      AL(y.router, (size_t)s.experts * W * 4);
+      AL(y.moe_in, (size_t)s.experts * 2 * s.ff * W * wsz);
+      AL(y.moe_out, (size_t)s.experts * W * s.ff * wsz);
+      h->moe = true;
+      h->E = std::max(h->E, s.experts);
+      h->topk = std::max(h->topk, s.top);
+      h->F = std::max(h->F, s.ff);
+    }
+    // extents the shared workspace is sized by (forward.cu ensure_workspace)
+    qkv_cols = std::max(qkv_cols, std::max(y.n_in, y.q_cols));
+    q_cols = std::max(q_cols, std::max(s.heads * y.Dk, y.ov_p));
+    h->nh = std::max(h->nh, s.heads);
+    h->hd = std::max(h->hd, s.kv_rank);
+  }
+#undef AL
+  h->F = std::max(h->F, 8);
+  h->nkv = 1;
+  h->qkv_cols = qkv_cols;
+  h->q_cols = q_cols;
+  h->w1_cols = 0;
+  *out = h;
+  return NVLLM_OK;
+}
+
+extern "C" int nvllm_set_named_weight(nvllm_handle* h, const char* name, int dtype, const void* host_data,
+                                      const int64_t* shape, int ndim) {
+  if (!h) return NVLLM_ERR_INVALID;
+  return layered_set_weight(h, name, dtype, host_data, shape, ndim);
+}

@@ -124,7 +124,7 @@ gemv_kernel(const AT* __restrict__ A, int lda, const WT* __restrict__ W, int N, 
             g += hrow[0];
             u += hrow[1];
           }
-          y = silu(g) * u;
+          y = glu_unit(g, u, pre.glu_limit);
         } else {
           float hsum = 0.f;
           for (int sl = 0; sl < pre.Sh; sl++) hsum += pre.hp[(size_t)sl * pre.hstride + (size_t)m * pre.hld + col];

@@ -70,6 +70,7 @@ struct Tc5Fuse {
   float m;
   const float* g;  // weight of the norm that reads x next: xb = bf16(x * g); null = ones
   int cl;          // > 1: the S k-splits of an output tile are one thread-block cluster of `cl` CTAs
+  float glu_limit; // > 0: the gated epilogue computes the clamped unit (common.cuh glu_unit)
 };
 // A second GEMM chained behind the first inside ONE launch (the FFN pair of a decode step:
 // W1 + activation, then W2): every CTA runs its units of problem 1, then its units of problem 2.
@@ -540,7 +541,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const float send = __uint_as_float(odd ? r[c] : r[c + 16]);
             const float got = __shfl_xor_sync(0xffffffffu, send, 1);
             const float g = alpha * (odd ? got : mine), u = alpha * (odd ? mine : got);
-            const float v = __fdividef(g, 1.0f + __expf(-g)) * u;
+            const float v = fz.glu_limit > 0.f ? glu_unit(g, u, fz.glu_limit)
+                                               : __fdividef(g, 1.0f + __expf(-g)) * u;
             *reinterpret_cast<bf16*>(stg + (c + (odd ? 16 : 0)) * 48 + p * 2) =
                 __float2bfloat16_rn(v);
           }
@@ -1004,7 +1006,7 @@ static cudaError_t launch_bt(cudaStream_t st, const Tc5Args& a, const TmaDesc* t
   int grid = min(sc.units, max(1, sm_counts[dev]));
   if (a.max_ctas > 0 && a.epi != TC5_EPI_RESID) grid = max(1, min(grid, a.max_ctas));
   Tc5Fuse fz{a.rs_ssq, a.rs_parts, a.rs_ld, a.rs_inv_h, a.rs_eps, a.res_x, (bf16*)a.res_xb, a.res_ssq,
-             a.res_ssq_ld, a.res_bias, a.res_m, a.res_g, CL ? sc.S : 0};
+             a.res_ssq_ld, a.res_bias, a.res_m, a.res_g, CL ? sc.S : 0, a.glu_limit};
   if (a.epi == TC5_EPI_RESID) {
     if (!a.res_x || !a.res_xb || !a.res_ssq || a.g_experts > 0) return cudaErrorInvalidValue;
     // split-K only as a cluster: one CTA per unit, one token tile, cluster = the S splits of a tile

@@ -33,10 +33,37 @@ struct LayerW {
         *m_d = nullptr, *m_norm = nullptr;
 };
 
+// A layer of a model given as a list of layers (nvllm_create_layered): its sizes, its tensors
+// in device layout ([out, in], inner extents padded to 8 with zeros) and where its cached rows live.
+struct ListedLayer {
+  nvllm_layer_spec s{};
+  int Dk = 0;        // cached row: kv_rank + rot_dim
+  int n_in = 0;      // rows of the fused input projection [dq | dkv (own cache only) | g]
+  int q_cols = 0;    // heads * (dim + rot_dim)
+  int q_rank_p = 0;  // q_rank rounded up to 8 (K of the query up projection)
+  int ov_p = 0;      // heads * vdim rounded up to 8 (K of the output projection)
+  int pool = -1;     // index of the cache pool this layer reads (its own, or its source layer's)
+  int rope = -1;     // index of its rotation table
+  float* norm_w = nullptr;
+  void* w_in = nullptr;
+  float *dq_norm = nullptr, *dkv_norm = nullptr;
+  void *w_uq = nullptr, *w_uk = nullptr, *w_uv = nullptr, *w_o = nullptr;
+  void *w1 = nullptr, *w2 = nullptr;  // dense feed-forward: [2 ff, W] gate / up interleaved, [W, ff]
+  float* router = nullptr;            // [experts, W] fp32
+  void *moe_in = nullptr, *moe_out = nullptr;  // [experts, 2 ff, W] interleaved, [experts, W, ff]
+};
+struct RopeTable {
+  double base = 0;
+  int dims = 0;
+  double* inv_freq = nullptr;  // [dims / 2] on the device
+  float *cosT = nullptr, *sinT = nullptr;  // [T_cap, dims / 2] of the current step's rows
+};
+
 // one engine step's integer inputs, packed in a single pinned host buffer and copied with
 // one cudaMemcpyAsync; the device pointers below point into the device mirror
 struct StepLayout {
   int T = 0, n = 0, max_blocks = 0, n_qtiles = 0;
+  int n_out = 0;  // rows that go through the final norm and the LM head: n last rows + requested ones
   bool prefill = false;
   int max_len = 0;        // longest context (incl. new tokens) in the step
   long long sum_len = 0;  // sum of contexts (attention bytes accounting)
@@ -84,6 +111,10 @@ struct Workspace {
   float* topk_w = nullptr;
   MoeSortBufs sort{};
   int max_tiles = 0;
+  // latent attention (forward_layered.cu)
+  void* lat_cq = nullptr;     // [T, max q_rank_p] act dtype
+  float* lat_gate = nullptr;  // [T, max heads]
+  void* lat_o = nullptr;      // [T, max heads * kv_rank] act dtype
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order
@@ -140,6 +171,16 @@ struct nvllm_handle {
   int n_mamba = 0;
   int m_nh = 0, m_hd = 0, m_N = 0, m_G = 0, m_K = 0, m_E = 0, m_conv = 0, m_P = 0;
   float* ssm_pool = nullptr;
+  // model given as a list of layers (nvllm_create_layered, forward_layered.cu)
+  bool layered = false;
+  std::vector<nvllm::ListedLayer> ll;
+  std::vector<void*> lat_pools;          // per cache-owning layer: [num_blocks * 256][Dk]
+  std::vector<nvllm::RopeTable> ropes;   // distinct (base, dims) of the layers
+  std::vector<std::string> named_got;    // tensors handed in so far (nvllm_set_named_weight)
+  float logit_softcap = 0.f;
+  float glu_limit_cur = 0.f;             // gated-unit variant of the GEMM being issued (forward_ops.h)
+  std::vector<int32_t> want_rows;        // rows of the next step whose logits were asked for
+  int fetched_rows = 0;                  // ... and how many the last step produced
   // weights
   void *wte = nullptr, *wpe = nullptr, *lm_head = nullptr;
   bool lm_head_owned = false;
@@ -243,6 +284,11 @@ extern thread_local std::string g_create_error;
 void free_workspace(nvllm_handle* h);
 int ensure_workspace(nvllm_handle* h, int T, int n);
 int forward_step(nvllm_handle* h);  // runs h->lay
+int forward_step_layered(nvllm_handle* h);  // forward_layered.cu
+int layered_set_weight(nvllm_handle* h, const char* name, int dtype, const void* host,
+                       const int64_t* shape, int ndim);
+int layered_finalize(nvllm_handle* h);
+void layered_free(nvllm_handle* h);
 int forward_step_auto(nvllm_handle* h);  // forward_step, or the two-chunk tensor-parallel prefill pipeline
 int prof_collect(nvllm_handle* h);
 

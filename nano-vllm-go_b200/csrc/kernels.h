@@ -31,6 +31,14 @@ cudaError_t launch_embed(cudaStream_t st, int wdt, const int* tokens, const int*
                          const void* wte, const void* wpe, int max_pos, float mult, float* x, int T,
                          int H, void* xb = nullptr, float* ssq = nullptr, const float* g = nullptr);
 
+// Variants of the top-k routing rule.  Default (all zero): weights renormalised over the chosen
+// experts (moe.go:88-103).  groups > 0: the experts form `groups` equal groups of neighbours, a
+// group scores as its best expert and only the `keep` best groups may be chosen from.
+// raw != 0: the weights are the chosen experts' softmax scores times `scale`, not renormalised.
+struct RouteOpts {
+  int groups, keep, raw;
+  float scale;
+};
 struct NormArgs {
   float* x;            // [*, H] residual stream, updated in place when p1/p2 given
   const float* p1;     // partials [S1][rows_total][H] or null
@@ -46,6 +54,7 @@ struct NormArgs {
   const float* bias2;
   const float* w;      // [H]; null = all ones (the weight is folded into the next GEMM)
   const float* b;      // [H] or null => RMSNorm (tensor.go:197)
+  int centered;        // b == null but still a LayerNorm: (x - mean) / sqrt(var + eps) * w
   float eps;
   void* y;             // [n_rows, H] dtype ydt (may be null: residual update only)
   int ydt;
@@ -67,13 +76,16 @@ struct NormArgs {
   int E, topk;
   int* topk_idx;
   float* topk_w;
+  RouteOpts route;
 };
 cudaError_t launch_norm(cudaStream_t st, const NormArgs& a);
 
 // SwiGLU: out[t,j] = silu(h[t,j]) * h[t,F+j]   (transformer.go:50-66, mamba2.go:360-367)
 // GELU:   out[t,j] = gelu_tanh(h[t,j] + b1[j]) (transformer.go:67-78, tensor.go:181-190)
+// glu_limit > 0 (with swiglu): the clamped gated unit g = min(gate, limit), u = clamp(up, +-limit),
+// out = g * sigmoid(1.702 g) * (u + 1)
 cudaError_t launch_act(cudaStream_t st, int odt, int T, int F, const float* h, int S, size_t stride,
-                       const float* bias, int swiglu, void* out);
+                       const float* bias, int swiglu, void* out, float glu_limit = 0.f);
 
 // Sum split-K partials (+bias), RoPE rotate_half on Q and K (rope.go:153-205), write Q
 // [T, nh*hd] (dtype qdt) and scatter K,V into the paged pool (dtype kvdt) at slots[t].
@@ -182,6 +194,7 @@ struct GemvPre {
   int hld;
   const float* hbias;  // [K] (GELU branch) or null
   int swiglu;
+  float glu_limit;     // > 0 with swiglu: the clamped gated unit (see launch_act)
 };
 // split-K slices a skinny GEMV will produce for (M,N,K); workspace must hold S*M*N floats
 int gemv_splits(int M, int N, int K);
@@ -213,6 +226,7 @@ struct Tc5Args {
   void* epi_out;        // bf16 [M, epi_ld]
   int epi_ld;
   const float* epi_bias;  // [N] or null (GELU)
+  float glu_limit;        // TC5_EPI_SWIGLU: > 0 selects the clamped gated unit (see launch_act)
   // ---- RMSNorm folded into the GEMMs (forward.cu "fold"): the producer of x writes
   // bf16(x * g) (g = norm weight), the row statistic is applied to the accumulator.
   // consumer side, rs_ssq != null: A holds bf16(x * g), not yet divided by the row's rms, and every
@@ -332,6 +346,50 @@ cudaError_t launch_attn_prefill_tc5(cudaStream_t st, const AttnArgs& a);
 bool attn_decode_t_supported(const AttnArgs& a);
 cudaError_t launch_attn_decode_t(cudaStream_t st, const AttnArgs& a);
 
+// ---------------------------------------------------------------- attention_latent.cu
+// Latent attention: per token the pool holds one row [c (R) | rotated shared key part (rot)]
+// for all heads; queries are absorbed through W_uk and values expanded through W_uv after the
+// weighted sum (see attention_latent.cu).  One struct carries the layer's sizes and the
+// buffers of its four kernels.
+constexpr int LAT_QTILE = 16;  // new tokens per attention tile (the host builds the tile list)
+struct LatentArgs {
+  int T, H, dim, rot, rot_dims, vdim, R, q_rank, q_rank_p, ov_p;
+  int own_kv;            // the layer has its own key/value down projection (writes the pool)
+  float eps, scale;
+  // fused input projection [dq | dkv | g]: split-K partials [S][T][in_ld]
+  const float* in_p; int in_S; size_t in_stride; int in_ld;
+  const float *dq_norm, *dkv_norm;   // [q_rank], [R] fp32
+  const float *cosT, *sinT;          // [T, rot_dims / 2] of the step's rows
+  const int* slots;                  // [T] pool row of each new token
+  void* pool;                        // [blocks * 256][R + rot] cache dtype
+  void* cq;                          // [T, q_rank_p] act dtype (zero padded)
+  float* gate;                       // [T, H] sigmoid of the head gates
+  // query up projection partials [S][T][q_ld], W_uk [H * dim, R], absorbed queries [T, H, R + rot]
+  const float* q_p; int q_S; size_t q_stride; int q_ld;
+  const void* w_uk;
+  void* qabs;
+  // attention
+  const int* block_tables; int max_blocks;
+  const int *cu_q, *seq_start, *tile_seq, *tile_q0;
+  int n_tiles, qtile, n_splits;
+  float* split_ws;                   // [T, H, n_splits, R + 2]
+  void* olat;                        // [T, H, R] act dtype
+  // output
+  const void* w_uv;                  // [H * vdim, R]
+  void* attn_out;                    // [T, ov_p] act dtype
+};
+cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int half,
+                              const double* inv_freq, float* cosT, float* sinT);
+cudaError_t launch_latent_prep(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a);
+cudaError_t launch_latent_q(cudaStream_t st, int qdt, int wdt, const LatentArgs& a);
+int latent_attn_qtile();
+int latent_attn_splits(int n_seqs, int H, int max_len, int sm_count);
+cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a);
+cudaError_t launch_latent_out(cudaStream_t st, int qdt, int wdt, const LatentArgs& a);
+// out[i] = cap * tanh(sum_s p[s * stride + i] / cap)   (cap <= 0: plain sum)
+cudaError_t launch_softcap(cudaStream_t st, const float* p, int S, size_t stride, size_t n, float cap,
+                           float* out);
+
 // ---------------------------------------------------------------- mamba.cu
 // Mamba2 block between its two projections (mamba2.go:72-351), ragged batch
 struct MambaArgs {
@@ -360,7 +418,7 @@ cudaError_t launch_mamba_gate_norm(cudaStream_t st, const MambaArgs& a, int odt,
 // Router: probs = softmax(x @ R) over all E, top-k (descending), weights renormalised
 // (moe.go:63-103).  x fp32 [T,H]; R fp32 [E,H].
 cudaError_t launch_moe_router(cudaStream_t st, const float* x, const float* R, int T, int H, int E,
-                              int k, int* topk_idx, float* topk_w);
+                              int k, int* topk_idx, float* topk_w, RouteOpts ro = RouteOpts{});
 // Group the T*k (token,slot) pairs by expert into `tile`-row tiles.
 struct MoeSortBufs {
   int* counts;       // [E]
@@ -386,7 +444,8 @@ cudaError_t launch_moe_gather(cudaStream_t st, int rows, int H, const void* x, c
                               void* xs);
 // g[row, j] = silu(h[row, 2j]) * h[row, 2j + 1] (gate / up interleaved at load) with the fp32
 // sigmoid of moe.go:203-212
-cudaError_t launch_moe_glu(cudaStream_t st, int odt, int rows, int I, const float* h, void* g);
+cudaError_t launch_moe_glu(cudaStream_t st, int odt, int rows, int I, const float* h, void* g,
+                           float glu_limit = 0.f);
 // y[t,:] = sum_s w[t,s] * Y[pair_row[t*k+s], :]   (moe.go:116-118, slot order = descending prob)
 cudaError_t launch_moe_combine(cudaStream_t st, int T, int k, int H, const float* Y,
                                const int* pair_row, const float* topk_w, float* y);

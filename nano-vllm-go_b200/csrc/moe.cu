@@ -14,19 +14,19 @@ namespace nvllm {
 // not fuse it into the norm).
 __global__ void __launch_bounds__(128)
 moe_router_kernel(const float* __restrict__ x, const float* __restrict__ R, int H, int E, int k,
-                  int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+                  int* __restrict__ topk_idx, float* __restrict__ topk_w, RouteOpts ro) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float probs[MOE_MAX_E];
   const int t = blockIdx.x;
-  moe_route_row(x + (size_t)t * H, R, H, E, k, probs, (size_t)t, topk_idx, topk_w);
+  moe_route_row(x + (size_t)t * H, R, H, E, k, probs, (size_t)t, topk_idx, topk_w, ro);
 }
 
 cudaError_t launch_moe_router(cudaStream_t st, const float* x, const float* R, int T, int H, int E,
-                              int k, int* topk_idx, float* topk_w) {
+                              int k, int* topk_idx, float* topk_w, RouteOpts ro) {
   if (T <= 0) return cudaSuccess;
   if (E > MOE_MAX_E || k > 32 || k > E || (H % 8) != 0) return cudaErrorInvalidValue;
-  (void)launch_k(moe_router_kernel, dim3(T), dim3(128), 0, st, x, R, H, E, k, topk_idx, topk_w);
+  (void)launch_k(moe_router_kernel, dim3(T), dim3(128), 0, st, x, R, H, E, k, topk_idx, topk_w, ro);
   return cudaGetLastError();
 }
 
@@ -249,7 +249,7 @@ cudaError_t launch_moe_sort_gather(cudaStream_t st, const int* topk_idx, int T, 
 // h[row, 2j] is gate j and h[row, 2j + 1] is up j.
 template <typename OT>
 __global__ void moe_glu_kernel(size_t nvec, int I, const float* __restrict__ h,
-                               OT* __restrict__ g) {
+                               OT* __restrict__ g, float glu_limit) {
   pdl_launch_dependents();
   pdl_wait();
   const int vpr = I / 8;
@@ -264,22 +264,27 @@ __global__ void moe_glu_kernel(size_t nvec, int I, const float* __restrict__ h,
     for (int i = 0; i < 8; i++) {
       const float a = i < 4 ? lo[2 * i] : hi[2 * i - 8];
       const float u = i < 4 ? lo[2 * i + 1] : hi[2 * i - 7];
-      const float sig = 1.0f / (1.0f + expf(-a));
-      o[i] = a * sig * u;
+      if (glu_limit > 0.f) {
+        o[i] = glu_unit(a, u, glu_limit);
+      } else {
+        const float sig = 1.0f / (1.0f + expf(-a));
+        o[i] = a * sig * u;
+      }
     }
     store8(g + row * I + j, o);
   }
 }
 
-cudaError_t launch_moe_glu(cudaStream_t st, int odt, int rows, int I, const float* h, void* g) {
+cudaError_t launch_moe_glu(cudaStream_t st, int odt, int rows, int I, const float* h, void* g,
+                           float glu_limit) {
   if (rows <= 0) return cudaSuccess;
   if ((I % 8) != 0) return cudaErrorInvalidValue;
   size_t nvec = (size_t)rows * (I / 8);
   int blocks = (int)min((size_t)148 * 16, (nvec + 255) / 256);
   if (odt == DT_F32)
-    (void)launch_k(moe_glu_kernel<float>, dim3(blocks), dim3(256), 0, st, nvec, I, h, (float*)g);
+    (void)launch_k(moe_glu_kernel<float>, dim3(blocks), dim3(256), 0, st, nvec, I, h, (float*)g, glu_limit);
   else
-    (void)launch_k(moe_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, st, nvec, I, h, (bf16*)g);
+    (void)launch_k(moe_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, st, nvec, I, h, (bf16*)g, glu_limit);
   return cudaGetLastError();
 }
 

@@ -2,6 +2,7 @@
 // kernel (moe.cu) and the norm kernel that fuses it (elementwise.cu).
 #pragma once
 #include "common.cuh"
+#include "kernels.h"
 
 namespace nvllm {
 
@@ -16,7 +17,8 @@ constexpr int MOE_MAX_E = 256;
 __device__ __forceinline__ void moe_route_row(const float* y, const float* __restrict__ R, int H,
                                               int E, int k, float* probs, size_t t,
                                               int* __restrict__ topk_idx,
-                                              float* __restrict__ topk_w) {
+                                              float* __restrict__ topk_w,
+                                              RouteOpts ro = RouteOpts{}) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   // Two experts per pass with the k loop unrolled four deep: up to 8 independent 32-byte loads
   // of R per lane in flight, so the E / nw passes cost one L2 round trip each instead of one
@@ -75,6 +77,26 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
   __syncwarp();
   for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
   __syncwarp();
+  // group-limited choice: a group scores as its best expert; group g stays iff fewer than
+  // `keep` groups beat it (higher score, or equal score and lower index).  Experts of the other
+  // groups are taken out of the selection below (their probabilities are not needed again).
+  if (ro.groups > 1 && ro.keep < ro.groups) {
+    __shared__ float gsc[MOE_MAX_E];
+    const int per = E / ro.groups;
+    for (int g = lane; g < ro.groups; g += 32) {
+      float b = -1.f;
+      for (int j = 0; j < per; j++) b = fmaxf(b, probs[g * per + j]);
+      gsc[g] = b;
+    }
+    __syncwarp();
+    for (int g = lane; g < ro.groups; g += 32) {
+      int beat = 0;
+      for (int o = 0; o < ro.groups; o++) beat += (gsc[o] > gsc[g] || (gsc[o] == gsc[g] && o < g)) ? 1 : 0;
+      if (beat >= ro.keep)
+        for (int j = 0; j < per; j++) probs[g * per + j] = -2.f;
+    }
+    __syncwarp();
+  }
   float sel_p = 0.f;  // lane s keeps the s-th selection (k <= 32)
   int sel_i = 0;
   float ksum = 0.f;
@@ -105,7 +127,7 @@ __device__ __forceinline__ void moe_route_row(const float* y, const float* __res
   }
   if (lane < k) {
     topk_idx[t * k + lane] = sel_i;
-    topk_w[t * k + lane] = sel_p / ksum;
+    topk_w[t * k + lane] = ro.raw ? sel_p * ro.scale : sel_p / ksum;
   }
 }
 

@@ -315,6 +315,7 @@ int nvllm_destroy(nvllm_handle* h) {
     F(w.m_d); F(w.m_norm);
     F(w.router); F(w.moe_in); F(w.moe_out);
   }
+  nvllm::layered_free(h);
   F(h->cosT);
   F(h->sinT);
   F(h->kpool);

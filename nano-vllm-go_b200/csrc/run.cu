@@ -31,9 +31,10 @@ static int ensure_stage(nvllm_handle* h, size_t words) {
 }
 
 // offsets of a step's arrays inside its staging buffer (every array 16-byte aligned)
-static void plan_layout(StepLayout& L, int T, int n, int max_blocks, int n_qtiles) {
+static void plan_layout(StepLayout& L, int T, int n, int max_blocks, int n_qtiles, int n_extra = 0) {
   L.T = T;
   L.n = n;
+  L.n_out = n + n_extra;
   L.max_blocks = max_blocks;
   L.n_qtiles = n_qtiles;
   size_t o = 0;
@@ -48,7 +49,7 @@ static void plan_layout(StepLayout& L, int T, int n, int max_blocks, int n_qtile
   L.cu_q = take(n + 1);
   L.seq_start = take(n);
   L.seq_len = take(n);
-  L.last_row = take(n);
+  L.last_row = take(n + n_extra);
   L.block_tables = take((size_t)n * max_blocks);
   L.tile_seq = take(n_qtiles);
   L.tile_q0 = take(n_qtiles);
@@ -241,7 +242,7 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
 
   // ---- pass 1: sizes and validation
   int T = 0, max_blocks = 0, n_qtiles = 0, max_len = 0;
-  const int qtile = attn_prefill_qtile(h->adt, h->kvdt, h->hd);
+  const int qtile = h->layered ? latent_attn_qtile() : attn_prefill_qtile(h->adt, h->kvdt, h->hd);
   long long sum_len = 0;
   double pairs = 0;
   for (int i = 0; i < n; i++) {
@@ -276,8 +277,16 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
     sum_len += len;
     pairs += 0.5 * ((double)len * (len + 1) - (double)start * (start + 1));
   }
+  // further rows whose logits the caller asked for (nvllm_request_logits), consumed by this step
+  std::vector<int32_t> want;
+  want.swap(h->want_rows);
+  h->fetched_rows = 0;
+  const int n_extra = (int)want.size();
+  if (n_extra && h->tp > 1) return set_err(h, NVLLM_ERR_INVALID, "requested logits rows need a single-GPU handle");
+  for (int r : want)
+    if (r < 0 || r >= T) return set_err(h, NVLLM_ERR_RANGE, "requested logits row %d outside the step's %d rows", r, T);
   StepLayout& L = h->lay;
-  plan_layout(L, T, n, max_blocks, is_prefill ? n_qtiles : 0);
+  plan_layout(L, T, n, max_blocks, is_prefill ? n_qtiles : 0, n_extra);
   L.prefill = is_prefill != 0;
   L.max_len = max_len;
   L.sum_len = sum_len;
@@ -285,7 +294,7 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
   int rc;
   if ((rc = ensure_stage(h, L.words))) return rc;
   L.d = h->d_stage;
-  if ((rc = ensure_workspace(h, T, n))) return rc;
+  if ((rc = ensure_workspace(h, T, n + n_extra))) return rc;
   if (!h->h_out || n > h->ws.n_cap_out) {
     NV_CHECK(h, cudaStreamSynchronize(h->stream));
     if (h->h_out) cudaFreeHost(h->h_out);
@@ -334,6 +343,7 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
     s_uni[i] = (t > 0.f) ? (uniforms ? uniforms[i] : next_uniform(h)) : 0.f;
   }
   s[L.cu_q + n] = row;
+  for (int i = 0; i < n_extra; i++) s[L.last_row + n + i] = want[i];
 
   cudaStream_t st = h->stream;
   // SampleWithHistory filters need every sequence's full token history on the device
@@ -410,10 +420,29 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
   h->resident_ok = true;
   h->run_lay = L;
   h->run_lay_ok = true;
+  h->fetched_rows = n_extra;
   fill_stats(h, stats, T, L.words * 4, d2h, true);
   if (stats) stats->used_graph = used_graph ? 1 : 0;
   remember_call(h, n, cu_seqlens, block_tables, cu_blocks);
   try_speculate(h, n, temperature);
+  return NVLLM_OK;
+}
+
+extern "C" int nvllm_request_logits(nvllm_handle* h, const int32_t* rows, int n_rows) {
+  if (!h || n_rows < 0 || (n_rows > 0 && !rows)) return NVLLM_ERR_INVALID;
+  h->want_rows.assign(rows, rows + n_rows);
+  return NVLLM_OK;
+}
+// The requested rows follow the n last rows in the step's logits matrix.
+extern "C" int nvllm_fetch_logits(nvllm_handle* h, float* out, int n_rows) {
+  if (!h || !out || n_rows < 0) return NVLLM_ERR_INVALID;
+  if (n_rows > h->fetched_rows)
+    return set_err(h, NVLLM_ERR_STATE, "%d rows asked for, the last step produced %d", n_rows, h->fetched_rows);
+  if (n_rows == 0) return NVLLM_OK;
+  NV_CHECK(h, cudaSetDevice(h->dev));
+  NV_CHECK(h, cudaStreamSynchronize(h->stream));
+  NV_CHECK(h, cudaMemcpy2D(out, (size_t)h->V * 4, h->ws.logits_final + (size_t)h->run_lay.n * h->ldl,
+                           (size_t)h->ldl * 4, (size_t)h->V * 4, n_rows, cudaMemcpyDeviceToHost));
   return NVLLM_OK;
 }
 

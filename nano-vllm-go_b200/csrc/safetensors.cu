@@ -335,6 +335,26 @@ struct Loader {
 
 int load_safetensors(nvllm_handle* h, const char* dir, int arch, uint64_t* bytes_out, int* tensors_out) {
   if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "load_safetensors after finalize");
+  if (arch == NVLLM_ARCH_DUGOPEL) {
+    // a layered handle knows every tensor by the file's own names; finalize reports what is missing
+    if (!h->layered) return set_err(h, NVLLM_ERR_INVALID, "this checkpoint family needs a handle of nvllm_create_layered");
+    Checkpoint ck;
+    std::string err;
+    if (!ck.open_dir(dir, &err)) return set_err(h, NVLLM_ERR_INVALID, "%s", err.c_str());
+    uint64_t bytes = 0;
+    int count = 0;
+    for (auto& kv : ck.tensors) {
+      const TensorRef& t = kv.second;
+      if (t.dtype < 0) return set_err(h, NVLLM_ERR_INVALID, "tensor %s has an unsupported dtype (F32 / F16 / BF16 only)", kv.first.c_str());
+      int rc = layered_set_weight(h, kv.first.c_str(), t.dtype, t.data, t.shape.data(), (int)t.shape.size());
+      if (rc) return rc;
+      bytes += t.nbytes;
+      count++;
+    }
+    if (bytes_out) *bytes_out = bytes;
+    if (tensors_out) *tensors_out = count;
+    return NVLLM_OK;
+  }
   const Mapping* mp = nullptr;
   switch (arch) {
     case NVLLM_ARCH_GPT2: mp = &kGPT2; break;

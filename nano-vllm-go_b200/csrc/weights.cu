@@ -58,6 +58,7 @@ int nvllm::set_weight_src(nvllm_handle* h, int id, int layer, int dtype, const v
   if (!host) return set_err(h, NVLLM_ERR_INVALID, "null weight pointer");
   if (dtype < 0 || dtype > 2) return set_err(h, NVLLM_ERR_INVALID, "bad dtype %d", dtype);
   if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "set_weight after finalize");
+  if (h->layered) return set_err(h, NVLLM_ERR_STATE, "this handle takes its tensors by name (nvllm_set_named_weight)");
   NV_CHECK(h, cudaSetDevice(h->dev));
   const int H = h->H, V = h->V;
   const bool model_level = id < 16;
@@ -271,6 +272,7 @@ extern "C" int nvllm_finalize(nvllm_handle* h) {
   if (!h) return NVLLM_ERR_INVALID;
   if (h->finalized) return set_err(h, NVLLM_ERR_STATE, "already finalized");
   NV_CHECK(h, cudaSetDevice(h->dev));
+  if (h->layered) return layered_finalize(h);
   auto have = [&](int layer, int id) { return h->have[(size_t)(layer + 1) * 64 + id] != 0; };
   auto need = [&](int layer, int id, const char* name) {
     if (have(layer, id)) return 0;

@@ -87,6 +87,13 @@ SIGNATURES = {
                                               ctypes.POINTER(ctypes.c_int32),
                                               ctypes.POINTER(ctypes.c_int32),
                                               ctypes.POINTER(ctypes.c_int64), _u64p, _u64p]),
+    "nvllm_create_layered": (ctypes.c_int, [ctypes.POINTER(C.CLayeredConfig), ctypes.POINTER(C.CLayerSpec),
+                                            ctypes.POINTER(ctypes.c_void_p)]),
+    "nvllm_set_named_weight": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int,
+                                              ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64),
+                                              ctypes.c_int]),
+    "nvllm_request_logits": (ctypes.c_int, [ctypes.c_void_p, _i32p, ctypes.c_int]),
+    "nvllm_fetch_logits": (ctypes.c_int, [ctypes.c_void_p, _f32p, ctypes.c_int]),
     "nvllm_set_graphs": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "nvllm_set_speculation": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "nvllm_get_config": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(C.CConfig)]),

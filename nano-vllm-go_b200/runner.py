@@ -69,6 +69,10 @@ class CudaModelRunner:
         self.cfg = cfg
         self.precision = precision
         self._h = ctypes.c_void_p()
+        if isinstance(cfg, C.ListedModelConfig):
+            self._init_listed(cfg, weights, precision, num_kv_blocks, device, max_num_seqs,
+                              max_batched_tokens, weight_dtype, sampling, model_dir)
+            return
         cc = cfg.to_c(precision, num_kv_blocks=num_kv_blocks, max_num_seqs=max_num_seqs,
                       max_batched_tokens=max_batched_tokens, device=device, tp_size=tp_size,
                       tp_rank=tp_rank)
@@ -108,7 +112,54 @@ class CudaModelRunner:
         self.last_stats = L.RunStats()
         self.last_logits: Optional[np.ndarray] = None
 
+    def _init_listed(self, cfg, weights, precision, num_kv_blocks, device, max_num_seqs,
+                     max_batched_tokens, weight_dtype, sampling, model_dir):
+        """A model given as a list of layers (config.ListedModelConfig): nvllm_create_layered,
+        tensors by checkpoint name — `weights` yields (name, ndarray) pairs, or the library
+        reads model_dir's safetensors itself."""
+        cc, specs = cfg.to_c(precision, num_kv_blocks=num_kv_blocks, max_num_seqs=max_num_seqs,
+                             max_batched_tokens=max_batched_tokens, device=device)
+        L.check(self._lib.nvllm_create_layered(ctypes.byref(cc), specs, ctypes.byref(self._h)))
+        self.loaded_bytes, self.loaded_tensors = 0, 0
+        try:
+            if model_dir is not None:
+                nb, nt = ctypes.c_uint64(), ctypes.c_int32()
+                L.check(self._lib.nvllm_load_safetensors(self._h, os.fsencode(model_dir), int(cfg.arch),
+                                                         ctypes.byref(nb), ctypes.byref(nt)), self._h)
+                self.loaded_bytes, self.loaded_tensors = nb.value, nt.value
+            else:
+                for name, arr in weights:
+                    self.set_named_weight(name, arr, weight_dtype)
+            L.check(self._lib.nvllm_finalize(self._h), self._h)
+            self.temperature = 0.0
+            if sampling is not None:
+                self.set_sampling_params(**sampling)
+        except Exception:
+            self.close()
+            raise
+        self.last_stats = L.RunStats()
+        self.last_logits = None
+
+    @classmethod
+    def from_dir(cls, model_dir: str, precision: int = C.PREC_BF16, **kw):
+        """NewTensorModelRunner(modelDir) for the architectures of config.ARCHITECTURES: the model
+        class comes from config.json, the tensors from the directory's safetensors."""
+        cfg = C.from_model_dir(model_dir)
+        return cls(cfg, None, precision=precision, model_dir=model_dir, **kw)
+
     # ---- weights -----------------------------------------------------------
+    def set_named_weight(self, name: str, arr: np.ndarray, weight_dtype: Optional[int] = None):
+        if weight_dtype == C.DT_BF16:
+            from .weights import to_bf16_bits
+            a, dt = to_bf16_bits(arr).reshape(arr.shape), C.DT_BF16
+        elif arr.dtype == np.uint16:
+            a, dt = np.ascontiguousarray(arr), C.DT_BF16
+        else:
+            a, dt = np.ascontiguousarray(arr, dtype=np.float32), C.DT_F32
+        shape = (ctypes.c_int64 * a.ndim)(*a.shape)
+        L.check(self._lib.nvllm_set_named_weight(self._h, name.encode(), dt,
+                                                 a.ctypes.data_as(ctypes.c_void_p), shape, a.ndim), self._h)
+
     def set_weight(self, wid: int, layer: int, arr: np.ndarray, weight_dtype: Optional[int] = None):
         if weight_dtype == C.DT_BF16:
             from .weights import to_bf16_bits
@@ -163,6 +214,17 @@ class CudaModelRunner:
         L.check(rc, self._h)
         self.last_logits = logits
         return out, logits
+
+    def request_logits(self, rows: Seq[int]) -> None:
+        """Ask the next run for the logits of these rows of the step (indices into its computed
+        tokens, sequence after sequence) on top of each sequence's last row."""
+        r = np.asarray(rows, dtype=np.int32)
+        L.check(self._lib.nvllm_request_logits(self._h, L._ip(r), len(r)), self._h)
+
+    def fetch_logits(self, n_rows: int) -> np.ndarray:
+        out = np.empty((n_rows, self.cfg.vocab_size), dtype=np.float32)
+        L.check(self._lib.nvllm_fetch_logits(self._h, L._fp(out), n_rows), self._h)
+        return out
 
     def run_resident(self) -> None:
         """One more decode step for the previous decode batch, fully device-resident."""
