@@ -1,0 +1,455 @@
+"""Dugopel (layers listed in config.json; latent attention, clamped gated feed-forward,
+group-limited mixture of experts, soft-capped logits) against the plain float64 restatement in
+tests/dugopel_ref.py.  Every test makes its own small configuration and random weights."""
+import copy
+import json
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from helpers import C, E, W
+import nvllm_pkg
+import dugopel_ref as ref
+
+gpu = pytest.mark.gpu
+BLOCK = C.KV_BLOCK_SIZE
+
+
+# ------------------------------------------------------------------ configurations
+def mixer(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=24, base=5000.0, rot_dims=None,
+          scale=None, kv_from=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+         "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims},
+         "scale": float((dim + rot_dim) ** -0.5 if scale is None else scale)}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def dense(ff=64, limit=1.5):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def moe(ff=32, limit=2.5, experts=8, top=3, count=4, keep=2, scale=1.7):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit},
+            "router": {"experts": experts, "top": top, "groups": {"count": count, "keep": keep}, "scale": scale}}
+
+
+def layer(m, mlp):
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def model(layers, vocab=203, width=64, eps=1e-5, emb=3.0, cap=12.0):
+    return {"architecture": "Dugopel", "vocab": vocab, "width": width, "embedding": {"scale": emb},
+            "norm": {"eps": eps}, "logit_softcap": cap, "layers": layers}
+
+
+def mixed_model(**kw):
+    """Own caches and borrowed ones, every feed-forward kind, sizes that differ layer to layer."""
+    return model([layer(mixer(), dense()),
+                  layer(mixer(heads=2, dim=8, rot_dim=16, vdim=16, kv_rank=24, q_rank=16, rot_dims=8, base=300.0), moe()),
+                  layer(mixer(kv_from=0), None),
+                  layer(mixer(heads=2, dim=8, rot_dim=16, vdim=16, kv_rank=24, q_rank=16, rot_dims=8, base=300.0,
+                              kv_from=1), moe(ff=16, experts=4, top=1, count=1, keep=1, scale=0.5)),
+                  layer(mixer(heads=5, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=40), dense(ff=24, limit=0.7))], **kw)
+
+
+def random_weights(cfg_json, seed, bf16=False, gain=1.0):
+    cfg = C.dugopel_from_json(cfg_json)
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in cfg.tensor_shapes().items():
+        if len(shape) == 1:
+            a = 1.0 + 0.2 * rng.standard_normal(shape)
+        elif name == "embed":
+            a = rng.standard_normal(shape)
+        else:
+            a = gain * rng.standard_normal(shape) / np.sqrt(shape[1])
+        if name.endswith("router"):
+            a = a * 4.0  # spread the expert scores
+        a = a.astype(np.float32)
+        w[name] = W.bf16_round(a) if bf16 else a
+    return cfg, w
+
+
+# ------------------------------------------------------------------ a small engine
+class Engine:
+    """Runner + the engine's block manager; steps are lists of (request id, new tokens, wanted places)."""
+
+    def __init__(self, cfg, weights, prec, num_blocks=8):
+        R = nvllm_pkg.sub("runner")
+        self.run = R.CudaModelRunner(cfg, weights.items(), precision=prec, num_kv_blocks=num_blocks, sampling=None)
+        self.bm = E.BlockManager(num_blocks, BLOCK)
+        self.live, self.done = {}, {}
+
+    def step(self, entries, decode=False):
+        """entries: [(id, tokens, want)].  decode=True issues a decode-shaped call (one token each)."""
+        seqs, cached, rows, row0 = [], [], [], 0
+        for rid, toks, want in entries:
+            seq = self.live.get(rid)
+            if seq is None:
+                seq = self.live[rid] = E.Sequence(toks, temperature=0.0)
+                self.done[rid] = 0
+            else:
+                for t in toks:
+                    seq.append_token(t)
+            self.bm.reserve(seq, len(seq))
+            seqs.append(seq)
+            cached.append(self.done[rid])
+            rows += [row0 + k for k in want]
+            row0 += len(toks)
+            self.done[rid] = len(seq)
+        if decode:
+            assert all(len(t) == 1 for _, t, _ in entries)
+            toks, logits = self.run.run_flat([s.token_ids for s in seqs], False, None,
+                                             [s.block_table for s in seqs], [0.0] * len(seqs), want_logits=True)
+            return logits, toks
+        self.run.request_logits(rows)
+        toks, _ = self.run.run_flat([s.token_ids for s in seqs], True, num_cached=cached,
+                                    block_tables=[s.block_table for s in seqs], temperature=[0.0] * len(seqs))
+        return self.run.fetch_logits(len(rows)), toks
+
+    def end(self, rid):
+        self.bm.deallocate(self.live.pop(rid))
+        self.done.pop(rid)
+
+    def close(self):
+        self.run.close()
+
+
+def tol(prec):
+    return 2e-4 if prec == C.PREC_FP32 else 3e-2
+
+
+def check(got, want, prec, what=""):
+    want = np.asarray(want)
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= tol(prec), f"{what}: relative error {err:.3g}"
+
+
+def prompt(cfg, n, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, cfg.vocab_size, n)]
+
+
+PRECS = [C.PREC_FP32, C.PREC_BF16]
+
+
+# ------------------------------------------------------------------ CPU: configuration and routing oracle
+def test_config_json_is_read_field_by_field():
+    j = mixed_model()
+    cfg = C.dugopel_from_json(j)
+    assert cfg.num_layers == 5 and cfg.hidden == 64 and cfg.vocab_size == 203
+    assert cfg.layers[2].kv_from == 0 and cfg.layers[0].kv_from == -1
+    assert cfg.layers[1].mlp == C.MLP_MOE and cfg.layers[1].groups == 4 and cfg.layers[1].keep_groups == 2
+    assert cfg.layers[1].rot_dims == 8 and cfg.layers[1].rot_dim == 16
+    assert cfg.layers[2].mlp == C.MLP_NONE and cfg.layers[4].limit == pytest.approx(0.7)
+    names = cfg.tensor_shapes()
+    assert "l2.mix.dkv" not in names and "l0.mix.dkv" in names
+    assert names["l1.mlp.e7.down"] == (64, 32) and "l3.mlp.e4.gate" not in names
+    with tempfile.TemporaryDirectory() as d:
+        json.dump(j, open(os.path.join(d, "config.json"), "w"))
+        assert C.from_model_dir(d) == cfg
+        json.dump({"architecture": "nope"}, open(os.path.join(d, "config.json"), "w"))
+        with pytest.raises(ValueError):
+            C.from_model_dir(d)
+
+
+def test_reference_routing_keeps_only_the_best_groups():
+    rc = {"experts": 8, "top": 3, "groups": {"count": 4, "keep": 2}, "scale": 2.0}
+    z = np.array([[5.0, 0.0, 4.0, 3.9, 4.5, 0.1, 3.0, 0.0]])
+    idx, wts = ref.route(z, np.eye(8), rc)
+    # groups {0,1} (5.0) and {4,5} (4.5) win; expert 2 and 3 of the third-best group are shut out
+    assert sorted(idx[0].tolist()) == [0, 4, 5]
+    s = ref.softmax(z)[0]
+    np.testing.assert_allclose(wts[0], s[idx[0]] * 2.0)
+    assert abs(wts[0].sum() - 2.0) > 0.1  # not renormalised
+
+
+def test_block_manager_reserve_grows_and_reuses():
+    bm = E.BlockManager(3, BLOCK)
+    a = E.Sequence([1] * 10, temperature=0.0)
+    bm.reserve(a, 10)
+    assert a.block_table == [0]
+    for _ in range(BLOCK):
+        a.append_token(2)
+    bm.reserve(a, len(a))
+    assert a.block_table == [0, 1]
+    b = E.Sequence([3] * 5, temperature=0.0)
+    bm.reserve(b, 5)
+    with pytest.raises(RuntimeError):
+        bm.reserve(b, BLOCK + 1)
+    bm.deallocate(a)
+    bm.reserve(b, BLOCK + 1)
+    assert b.block_table == [2, 1]  # a freed block is handed out again
+
+
+# ------------------------------------------------------------------ GPU: each mechanism alone
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("case", ["attention", "partial_rotation", "dense", "moe_groups", "moe_top1", "borrowed_cache",
+                                  "softcap_saturates", "mixed"])
+def test_whole_prompt_matches_reference(case, prec):
+    layers = {
+        "attention": [layer(mixer(), None)],
+        "partial_rotation": [layer(mixer(rot_dim=16, rot_dims=4, heads=1), None)],
+        "dense": [layer(mixer(heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=8, q_rank=8), dense(ff=40, limit=0.5))],
+        "moe_groups": [layer(mixer(), moe(experts=12, top=4, count=6, keep=2, scale=3.0))],
+        "moe_top1": [layer(mixer(), moe(experts=4, top=1, count=4, keep=4, scale=1.0))],
+        "borrowed_cache": [layer(mixer(), None), layer(mixer(kv_from=0), dense()), layer(mixer(kv_from=0), None)],
+        "softcap_saturates": [layer(mixer(), dense())],
+    }
+    j = mixed_model() if case == "mixed" else model(layers[case], cap=0.8 if case == "softcap_saturates" else 12.0,
+                                                     emb=1.0 if case == "dense" else 3.0)
+    cfg, w = random_weights(j, 11, bf16=prec == C.PREC_BF16)
+    toks = prompt(cfg, 45, 5)
+    want = ref.forward(j, w, toks)
+    eng = Engine(cfg, w, prec)
+    got, _ = eng.step([("a", toks, list(range(len(toks))))])
+    eng.close()
+    check(got, want, prec, case)
+
+
+@gpu
+def test_group_limit_and_raw_weights_change_the_result():
+    """The same weights routed without the group limit, or with renormalised weights, must differ."""
+    j = model([layer(mixer(), moe(experts=12, top=4, count=6, keep=2, scale=3.0))])
+    cfg, w = random_weights(j, 11)
+    toks = prompt(cfg, 30, 5)
+    want = ref.forward(j, w, toks)
+    j2 = copy.deepcopy(j)
+    j2["layers"][0]["mlp"]["router"]["groups"] = {"count": 1, "keep": 1}
+    assert np.abs(ref.forward(j2, w, toks) - want).max() > 1e-2
+
+
+# ------------------------------------------------------------------ GPU: cache, portions, batches
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+def test_prefill_against_token_by_token_decoding(prec):
+    j = mixed_model()
+    cfg, w = random_weights(j, 3, bf16=prec == C.PREC_BF16)
+    toks = prompt(cfg, 40, 9)
+    want = ref.forward(j, w, toks)
+    eng = Engine(cfg, w, prec)
+    got = [eng.step([("a", toks[:1], [0])])[0][0]]          # the very first token alone
+    for t in range(1, len(toks)):                             # decode-shaped calls from position 1 on
+        got.append(eng.step([("a", toks[t:t + 1], [0])], decode=True)[0][0])
+    eng.close()
+    check(np.stack(got), want, prec, "decode")
+
+
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("sizes", [[2] * 30, [17, 2, 31, 2, 8], [1, 59], [58, 2], [33, 27]])
+def test_portions_of_a_prompt(sizes, prec):
+    j = mixed_model()
+    cfg, w = random_weights(j, 4, bf16=prec == C.PREC_BF16)
+    toks = prompt(cfg, 60, 2)
+    want = ref.forward(j, w, toks)
+    eng = Engine(cfg, w, prec)
+    got, at = [], 0
+    for n in sizes:
+        got.append(eng.step([("a", toks[at:at + n], list(range(n)))])[0])
+        at += n
+    eng.close()
+    assert at == len(toks)
+    check(np.concatenate(got), want, prec, f"portions {sizes}")
+
+
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+def test_page_borders_in_prompts_and_in_decoding(prec):
+    """Portions that end just before, at and just after a page border; decoding across the next
+    one; the scores are sharpened so that single far keys carry the result."""
+    j = model([layer(mixer(scale=1.5), dense()), layer(mixer(scale=1.5, kv_from=0), moe())])
+    cfg, w = random_weights(j, 6, bf16=prec == C.PREC_BF16)
+    toks = prompt(cfg, 2 * BLOCK + 6, 8)
+    want = ref.forward(j, w, toks)
+    eng = Engine(cfg, w, prec, num_blocks=4)
+    got, at = [], 0
+    for n in [BLOCK - 1, 1, 1, 3, BLOCK - 9]:                # ends at 255, 256, 257, 260, 507
+        got.append(eng.step([("a", toks[at:at + n], list(range(n)))])[0])
+        at += n
+    while at < len(toks):                                    # 507 .. 517 one by one (border at 512)
+        got.append(eng.step([("a", toks[at:at + 1], [0])], decode=True)[0])
+        at += 1
+    eng.close()
+    check(np.concatenate(got), want, prec, "page borders")
+
+
+def last_query_probs(j, w, toks):
+    """Attention weights of the last token over all keys: one layer, one head, from the reference's parts."""
+    m, eps = j["layers"][0]["mixer"], j["norm"]["eps"]
+    mix = {k[len("l0.mix."):]: v for k, v in w.items() if k.startswith("l0.mix.")}
+    pos = np.arange(len(toks))
+    x = np.asarray(w["embed"], np.float64)[toks] * j["embedding"]["scale"]
+    h = ref.layer_norm_noshift(x, w["l0.norm1"], eps)
+    c, kr = ref.latent_kv(h, m, mix, pos, eps)
+    cq = ref.rms_norm(h[-1:] @ np.asarray(mix["dq"], np.float64).T, mix["dq.norm"], eps)
+    q = cq @ np.asarray(mix["uq"], np.float64).T
+    qr = ref.rotate_half(q[:, m["dim"]:], pos[-1:], m["rot"]["base"], m["rot"]["dims"])
+    s = ((c @ np.asarray(mix["uk"], np.float64).T) @ q[0, :m["dim"]] + kr @ qr[0]) * m["scale"]
+    return ref.softmax(s)
+
+
+@gpu
+def test_a_far_key_that_stands_out_is_found():
+    """Sharpened scores; a prompt is searched whose last token puts most of its weight on ONE key
+    more than a page back.  The result must follow that key, in a prompt and in decoding."""
+    j = model([layer(mixer(heads=1, scale=4.0), None)], cap=30.0)
+    cfg, w = random_weights(j, 21)
+    n = BLOCK + 40
+    for seed in range(200):
+        toks = prompt(cfg, n, seed)
+        p = last_query_probs(j, w, toks)
+        if p.argmax() < 30 and p.max() > 0.6:
+            break
+    else:
+        pytest.fail("no prompt with a dominant far key found")
+    want = ref.forward(j, w, toks)
+    other = list(toks)
+    other[int(p.argmax())] = (toks[int(p.argmax())] + 1) % cfg.vocab_size
+    assert np.abs(ref.forward(j, w, other)[-1] - want[-1]).max() > 1e-2  # that key carries the result
+    eng = Engine(cfg, w, C.PREC_FP32, num_blocks=4)
+    got, _ = eng.step([("a", toks, [n - 1])])
+    check(got, want[-1:], C.PREC_FP32, "far key in a prompt")
+    eng.step([("b", toks[:-1], [])])
+    got, _ = eng.step([("b", toks[-1:], [0])], decode=True)
+    eng.close()
+    check(got, want[-1:], C.PREC_FP32, "far key in decoding")
+
+
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+def test_unequal_requests_in_one_batch_equal_each_alone(prec):
+    j = mixed_model()
+    cfg, w = random_weights(j, 8, bf16=prec == C.PREC_BF16)
+    lens = {"a": 70, "b": 3, "c": 1, "d": 29}
+    toks = {k: prompt(cfg, n, i) for i, (k, n) in enumerate(lens.items())}
+    want = {k: ref.forward(j, w, t) for k, t in toks.items()}
+    eng = Engine(cfg, w, prec, num_blocks=8)
+    # step 1: portions of a and d, all of b; step 2: the rest of a, one decoded token of d, all of c
+    g1, _ = eng.step([("a", toks["a"][:50], [0, 49]), ("b", toks["b"], [0, 1, 2]), ("d", toks["d"][:28], [27])])
+    g2, _ = eng.step([("d", toks["d"][28:], [0]), ("a", toks["a"][50:], [0, 19]), ("c", toks["c"], [0])])
+    eng.close()
+    check(g1, np.stack([want["a"][0], want["a"][49], want["b"][0], want["b"][1], want["b"][2], want["d"][27]]), prec, "step 1")
+    check(g2, np.stack([want["d"][28], want["a"][50], want["a"][69], want["c"][0]]), prec, "step 2")
+
+
+@gpu
+def test_decode_batch_of_unequal_contexts():
+    j = mixed_model()
+    cfg, w = random_weights(j, 8)
+    toks = {"a": prompt(cfg, BLOCK + 5, 1), "b": prompt(cfg, 9, 2), "c": prompt(cfg, 2, 3)}
+    want = {k: ref.forward(j, w, t) for k, t in toks.items()}
+    eng = Engine(cfg, w, C.PREC_FP32, num_blocks=6)
+    eng.step([(k, t[:-1], []) for k, t in toks.items()])
+    got, _ = eng.step([(k, t[-1:], [0]) for k, t in toks.items()], decode=True)
+    eng.close()
+    check(got, np.stack([want[k][-1] for k in toks]), C.PREC_FP32, "decode batch")
+
+
+@gpu
+def test_pages_are_freed_and_used_again():
+    j = mixed_model()
+    cfg, w = random_weights(j, 12)
+    eng = Engine(cfg, w, C.PREC_FP32, num_blocks=3)
+    for i in range(4):  # every request needs two of the three pages
+        toks = prompt(cfg, BLOCK + 20 + i, 40 + i)
+        got, _ = eng.step([("r%d" % i, toks, [0, BLOCK - 1, BLOCK, len(toks) - 1])])
+        tables = list(eng.live["r%d" % i].block_table)
+        want = ref.forward(j, w, toks)[[0, BLOCK - 1, BLOCK, len(toks) - 1]]
+        check(got, want, C.PREC_FP32, f"request {i} on pages {tables}")
+        eng.end("r%d" % i)
+    eng.close()
+
+
+@gpu
+def test_long_decoding_through_the_resident_loop():
+    """300 greedy tokens across a page border, device-resident steps, against the reference fed
+    with the same tokens."""
+    j = model([layer(mixer(), dense()), layer(mixer(kv_from=0), moe())])
+    cfg, w = random_weights(j, 13)
+    R = nvllm_pkg.sub("runner")
+    run = R.CudaModelRunner(cfg, w.items(), precision=C.PREC_FP32, num_kv_blocks=3, sampling=None)
+    toks = prompt(cfg, 10, 3)
+    out, _ = run.run_flat([toks], True, [0], [[0, 1]], [0.0])
+    gen = [int(out[0])]
+    for _ in range(299):
+        run.run_resident()
+        gen.append(int(run.sync(1)[0][0]))
+    run.close()
+    full = toks + gen
+    want = ref.forward(j, w, full[:-1])
+    margin = np.sort(want, axis=-1)
+    sure = (margin[:, -1] - margin[:, -2]) > 1e-3      # ignore numerical ties
+    pred = want.argmax(-1)[len(toks) - 1:]
+    assert np.array_equal(pred[sure[len(toks) - 1:]], np.array(gen)[sure[len(toks) - 1:]])
+
+
+# ------------------------------------------------------------------ GPU: through the engine and from a directory
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+def test_greedy_generation_through_engine_and_scheduler(prec):
+    j = mixed_model()
+    cfg, w = random_weights(j, 14, bf16=prec == C.PREC_BF16)
+    R = nvllm_pkg.sub("runner")
+    run = R.CudaModelRunner(cfg, w.items(), precision=prec, num_kv_blocks=8, sampling=None)
+    eng = E.LLMEngine(E.EngineConfig(num_kvcache_blocks=8, eos=-1), run)
+    prompts = [prompt(cfg, n, 50 + n) for n in (5, 33, 1, 12)]
+    sp = E.SamplingParams(max_tokens=24, ignore_eos=True)
+    outs = eng.generate(prompts, sp, temperature=0.0)
+    eng.close()
+    for p, o in zip(prompts, outs):
+        assert len(o) == 24
+        want = ref.forward(j, w, p + o[:-1])[len(p) - 1:]
+        srt = np.sort(want, axis=-1)
+        sure = (srt[:, -1] - srt[:, -2]) > (1e-3 if prec == C.PREC_FP32 else 0.15)
+        assert sure.sum() >= 12
+        assert np.array_equal(want.argmax(-1)[sure], np.array(o)[sure])
+
+
+@gpu
+def test_trace_replay_from_a_model_directory():
+    """config.json + safetensors (bf16) -> registry -> loader -> replay with requests that come and go."""
+    from st_writer import write_safetensors
+    TR = nvllm_pkg.sub("trace")
+    j = mixed_model()
+    cfg, w = random_weights(j, 15, bf16=True)
+    a, b = prompt(cfg, 300, 1), prompt(cfg, 41, 2)
+    wa, wb = ref.forward(j, w, a), ref.forward(j, w, b)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:200], "want": [0, 199]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[200:299], "want": [56]}, {"id": "b", "tokens": b[:40], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[40:], "want": [0]}, {"id": "a", "tokens": a[299:], "want": [0]}], "end": ["a", "b"]},
+        {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [40]}], "end": ["c"]},
+    ]
+    for dtype, prec in (("float32", C.PREC_FP32), ("bfloat16", C.PREC_BF16)):
+        with tempfile.TemporaryDirectory() as d:
+            json.dump(j, open(os.path.join(d, "config.json"), "w"))
+            write_safetensors(os.path.join(d, "model.safetensors"), w, dtype="BF16")
+            said = []
+            TR.replay(d, dtype, os.path.join(d, "out"), 2 * BLOCK + 64, [json.dumps(s) for s in steps], echo=said.append)
+            assert said == ["done %d" % i for i in range(4)]
+            rd = lambda i: np.fromfile(os.path.join(d, "out", "%d.f32" % i), "<f4").reshape(-1, cfg.vocab_size)
+            check(rd(0), wa[[0, 199]], prec, "step 0")
+            check(rd(1), wa[[256]], prec, "step 1")
+            check(rd(2), np.stack([wb[40], wa[299]]), prec, "step 2")
+            check(rd(3), wb[[40]], prec, "step 3")
+
+
+@gpu
+def test_bad_configurations_are_refused():
+    R = nvllm_pkg.sub("runner")
+    L = nvllm_pkg.sub("lib")
+    for bad in (model([layer(mixer(kv_from=0), None)]),                       # borrows from itself
+                model([layer(mixer(), None), layer(mixer(kv_rank=48, kv_from=0), None)]),  # other cache size
+                model([layer(mixer(), moe(experts=8, top=5, count=4, keep=2))])):  # kept groups hold 4 < top
+        cfg = C.dugopel_from_json(bad)
+        with pytest.raises(L.NvllmError):
+            R.CudaModelRunner(cfg, [], precision=C.PREC_FP32, num_kv_blocks=2, sampling=None)
+    cfg, w = random_weights(model([layer(mixer(), dense())]), 1)
+    w.pop("l0.mlp.up")
+    with pytest.raises(L.NvllmError, match="l0.mlp.up"):
+        R.CudaModelRunner(cfg, w.items(), precision=C.PREC_FP32, num_kv_blocks=2, sampling=None)
