@@ -18,8 +18,11 @@
 //                         optional key splits (decode) merged by latent_combine_kernel
 //  latent_out_kernel      head output = gate * W_uv (sum p c), written as the O projection's input
 // All arithmetic is fp32 (double for the angles); QT / KT are the activation / cache dtypes.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "mma.cuh"
 
 namespace nvllm {
 
@@ -198,7 +201,7 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
   const int q0 = a.tile_q0 ? a.tile_q0[tile] : 0;
   const int row0 = a.cu_q[seq];
   const int n_new = a.cu_q[seq + 1] - row0;
-  const int start = a.seq_start[seq];
+  const int start = a.tile_seq ? a.seq_start[seq] : a.seq_len[seq] - 1;  // decode steps advance seq_len only
   const int nq = min(a.qtile, n_new - q0);
   const int item0 = blockIdx.y * LAT_WARPS;
   if (item0 >= nq * a.H) return;
@@ -291,6 +294,222 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
   }
 }
 
+// ---------------------------------------------------------------- attention, tensor cores
+// bf16 path (Dk and R multiples of 16, R <= 8 * NR): the same items and key ranges as the kernel
+// above, 64 items per CTA (4 warps x 16 rows of mma.sync m16n8k16).  The tile's absorbed queries
+// are one contiguous [items, Dk] block; key tiles of 64 cached rows arrive by cp.async into a
+// padded tile (row stride Dk + 8: conflict-free ldmatrix), double-buffered when two fit.  Scores
+// S = Q K^T over all Dk columns; the weighted sum P V takes the first R columns of the SAME tile
+// (ldmatrix.trans), so a cached row is staged once for both.  Online softmax in the accumulator
+// layout; the P fragments come straight from the score accumulators.
+constexpr int LM_ROWS = 64, LM_KT = 64;
+template <int NR>
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int two_stage) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) uint8_t smem_lm[];
+  const int Dk = a.R + a.rot, ld = Dk + 8, cpr = Dk / 8;
+  const uint32_t sQ = smem_addr(smem_lm);
+  const uint32_t sK0 = sQ + LM_ROWS * ld * 2;
+  const uint32_t tile_bytes = LM_KT * ld * 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3, mi = lane >> 3, lr = lane & 7;
+  pdl_wait();
+  const int tile = blockIdx.x;
+  const int seq = a.tile_seq ? a.tile_seq[tile] : tile;
+  const int q0 = a.tile_q0 ? a.tile_q0[tile] : 0;
+  const int row0 = a.cu_q[seq];
+  const int n_new = a.cu_q[seq + 1] - row0;
+  const int start = a.tile_seq ? a.seq_start[seq] : a.seq_len[seq] - 1;  // decode steps advance seq_len only
+  const int nq = min(a.qtile, n_new - q0);
+  const int n_items = nq * a.H;
+  const int item0 = blockIdx.y * LM_ROWS;
+  if (item0 >= n_items) return;
+  const int last_q = min(nq - 1, (item0 + LM_ROWS - 1) / a.H);
+  const int kv_end = start + q0 + last_q + 1;
+  const int n_tiles_k = ceil_div(kv_end, LM_KT);
+  const int per = ceil_div(n_tiles_k, (int)gridDim.z);
+  const int kt0 = blockIdx.z * per, kt1 = min(n_tiles_k, kt0 + per);
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const bf16* pool = (const bf16*)a.pool;
+  const bf16* qsrc = (const bf16*)a.qabs + ((size_t)(row0 + q0) * a.H + item0) * Dk;
+  const int q_rows = min(LM_ROWS, n_items - item0);
+
+  auto load_keys = [&](int kt, int buf) {
+    const int k0 = kt * LM_KT;
+    const int nk = min(LM_KT, kv_end - k0);
+    const bf16* src = pool + ((size_t)bt[k0 / KV_BLOCK] * KV_BLOCK + (k0 % KV_BLOCK)) * Dk;
+    const uint32_t dst = sK0 + buf * tile_bytes;
+    for (int i = threadIdx.x; i < LM_KT * cpr; i += blockDim.x) {
+      const int r = i / cpr, c = i % cpr;
+      const bool ok = r < nk;
+      cp_async16(dst + (r * ld + c * 8) * 2, ok ? (const void*)(src + (size_t)r * Dk + c * 8) : (const void*)src, ok);
+    }
+    cp_async_commit();
+  };
+  for (int i = threadIdx.x; i < LM_ROWS * cpr; i += blockDim.x) {
+    const int r = i / cpr, c = i % cpr;
+    const bool ok = r < q_rows;
+    cp_async16(sQ + (r * ld + c * 8) * 2, ok ? (const void*)(qsrc + (size_t)r * Dk + c * 8) : (const void*)qsrc, ok);
+  }
+  if (kt0 < kt1) load_keys(kt0, 0);
+  else cp_async_commit();
+
+  // rows g and g + 8 of this warp's 16: the last key position each may see (-1: no such item)
+  int limit[2];
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int item = item0 + warp * 16 + g + 8 * i;
+    limit[i] = item < n_items ? start + q0 + item / a.H : -1;
+  }
+  float o[NR][4];
+#pragma unroll
+  for (int dn = 0; dn < NR; dn++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float scale_log2 = a.scale * 1.4426950408889634f;
+  const int nks = Dk / 16, nrt = a.R / 8;
+
+  int buf = 0;
+  for (int kt = kt0; kt < kt1; kt++) {
+    const bool more = kt + 1 < kt1;
+    if (two_stage && more) {
+      load_keys(kt + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t sK = sK0 + (two_stage ? buf : 0) * tile_bytes;
+    const int kpos0 = kt * LM_KT;
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
+    for (int ks = 0; ks < nks; ks++) {
+      uint32_t q0r, q1r, q2r, q3r;
+      ldsm_x4(sQ + ((warp * 16 + lr + (mi & 1) * 8) * ld + (ks * 2 + (mi >> 1)) * 8) * 2, q0r, q1r, q2r, q3r);
+#pragma unroll
+      for (int nt = 0; nt < 8; nt += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(sK + ((nt * 8 + lr + (mi >> 1) * 8) * ld + (ks * 2 + (mi & 1)) * 8) * 2, b0, b1, b2, b3);
+        mma16816(s[nt], q0r, q1r, q2r, q3r, b0, b1);
+        mma16816(s[nt + 1], q0r, q1r, q2r, q3r, b2, b3);
+      }
+    }
+    // causal mask (keys past the CTA's range are zero-filled and masked the same way)
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+      const int kp = kpos0 + nt * 8 + 2 * t;
+      if (kp > limit[0]) s[nt][0] = -INFINITY;
+      if (kp + 1 > limit[0]) s[nt][1] = -INFINITY;
+      if (kp > limit[1]) s[nt][2] = -INFINITY;
+      if (kp + 1 > limit[1]) s[nt][3] = -INFINITY;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++) mx = fmaxf(mx, fmaxf(s[nt][2 * i], s[nt][2 * i + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[i], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f((m[i] - m_use) * scale_log2);  // m = -inf => 0
+      m[i] = m_new;
+      l[i] *= corr;
+#pragma unroll
+      for (int dn = 0; dn < NR; dn++) {
+        o[dn][2 * i] *= corr;
+        o[dn][2 * i + 1] *= corr;
+      }
+      float rs = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++) {
+        const float p0 = exp2f((s[nt][2 * i] - m_use) * scale_log2);
+        const float p1 = exp2f((s[nt][2 * i + 1] - m_use) * scale_log2);
+        s[nt][2 * i] = p0;
+        s[nt][2 * i + 1] = p1;
+        rs += p0 + p1;
+      }
+      l[i] += rs;  // per-thread partial; the quad is reduced once at the end
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {
+      const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      const uint32_t a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int dn = 0; dn < NR; dn += 2) {
+        if (dn < nrt) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(sK + ((kk * 16 + lr + (mi & 1) * 8) * ld + (dn + (mi >> 1)) * 8) * 2, b0, b1, b2, b3);
+          mma16816(o[dn], a0, a1, a2, a3, b0, b1);
+          mma16816(o[dn + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // the tile may be overwritten from here on
+    if (!two_stage && more) load_keys(kt + 1, 0);
+    buf ^= 1;
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int item = item0 + warp * 16 + g + 8 * i;
+    if (item >= n_items) continue;
+    const size_t it = (size_t)(row0 + q0) * a.H + item;  // row * H + head
+    if (gridDim.z == 1) {
+      const float inv = 1.0f / l[i];
+      bf16* op = (bf16*)a.olat + it * a.R;
+#pragma unroll
+      for (int dn = 0; dn < NR; dn++)
+        if (dn < nrt)
+          *reinterpret_cast<uint32_t*>(op + dn * 8 + 2 * t) = pack_bf16(o[dn][2 * i] * inv, o[dn][2 * i + 1] * inv);
+    } else {
+      float* rec = a.split_ws + (it * gridDim.z + blockIdx.z) * (a.R + 2);
+#pragma unroll
+      for (int dn = 0; dn < NR; dn++)
+        if (dn < nrt) {
+          rec[dn * 8 + 2 * t] = o[dn][2 * i];
+          rec[dn * 8 + 2 * t + 1] = o[dn][2 * i + 1];
+        }
+      if (t == 0) {
+        rec[a.R] = m[i] * a.scale;  // the combine kernel works on scaled scores
+        rec[a.R + 1] = l[i];
+      }
+    }
+  }
+}
+
+static bool latent_mma_enabled() {
+  static const bool on = !(getenv("NVLLM_LATENT_MMA") && atoi(getenv("NVLLM_LATENT_MMA")) == 0);
+  return on;
+}
+static bool latent_mma_ok(int qdt, int kvdt, const LatentArgs& a) {
+  return latent_mma_enabled() && qdt == DT_BF16 && kvdt == DT_BF16 && ((a.R + a.rot) % 16) == 0 && (a.R % 16) == 0 &&
+         a.R <= 256 && a.scale > 0.f;
+}
+template <int NR>
+static cudaError_t launch_latent_mma(cudaStream_t st, const LatentArgs& a, int ns) {
+  const int Dk = a.R + a.rot;
+  const size_t one = (size_t)LM_KT * (Dk + 8) * 2;
+  const int two = 3 * one <= 200 * 1024 ? 1 : 0;
+  const size_t smem = one * (two ? 3 : 2);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, LM_ROWS), ns);
+  (void)launch_k(latent_attn_mma_kernel<NR>, grid, dim3(128), smem, st, a, two);
+  return cudaGetLastError();
+}
+
 template <typename QT>
 __global__ void latent_combine_kernel(LatentArgs a, int n_splits) {
   pdl_launch_dependents();
@@ -331,6 +550,13 @@ cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentA
   const size_t smem = ((size_t)LAT_KT * (Dk + 1) + (size_t)LAT_WARPS * Dk) * sizeof(float);
   const int ns = max(1, a.n_splits);
   dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, LAT_WARPS), ns);
+  if (latent_mma_ok(qdt, kvdt, a)) {
+    cudaError_t e = a.R <= 64 ? launch_latent_mma<8>(st, a, ns)
+                    : a.R <= 128 ? launch_latent_mma<16>(st, a, ns) : launch_latent_mma<32>(st, a, ns);
+    if (e != cudaSuccess) return e;
+    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+    return cudaGetLastError();
+  }
   if (qdt == DT_F32 && kvdt == DT_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(latent_attn_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -239,7 +239,7 @@ int forward_step_layered(nvllm_handle* h) {
     a.cq = w.lat_cq; a.gate = w.lat_gate;
     a.w_uk = y.w_uk; a.qabs = w.q;
     a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
-    a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start;
+    a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
     a.olat = w.lat_o; a.w_uv = y.w_uv; a.attn_out = w.attn_out;
     a.split_ws = w.attn_ws;
     if (L.prefill) {
