@@ -453,6 +453,127 @@ def tp_leg(dist, rank, world, device, steps, warmup, barrier):
     return out
 
 
+# ---- --design dugopel: the layer-listed design beside the closest uniform model at equal size
+def dugopel_cfg(width, n_layers, heads, dim, rot_dim, vdim, kv_rank, q_rank, ff, vocab, moe=None, share=0):
+    """share > 0: of every `share` consecutive layers only the first has its own latent cache."""
+    layers = []
+    for l in range(n_layers):
+        kw = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank,
+                  rot_base=10000.0, rot_dims=rot_dim, scale=float((dim + rot_dim) ** -0.5),
+                  kv_from=(l - l % share) if share and l % share else -1)
+        if moe and l > 0:
+            kw.update(mlp=C.MLP_MOE, ff=ff, limit=7.0, experts=moe[0], top=moe[1], groups=moe[2],
+                      keep_groups=moe[3], router_scale=2.5)
+        else:
+            kw.update(mlp=C.MLP_DENSE, ff=ff if not moe else ff * moe[1], limit=7.0)
+        layers.append(C.LayerSpec(**kw))
+    return C.ListedModelConfig("dugopel", vocab, width, tuple(layers), 1e-5, embedding_scale=1.0,
+                               logit_softcap=30.0)
+
+
+def dugopel_device_weights(cfg, device, seed=1234):
+    import torch
+    g = torch.Generator(device=f"cuda:{device}")
+    for i, (name, shape) in enumerate(cfg.tensor_shapes().items()):
+        g.manual_seed(seed * 1000003 + i)
+        t = torch.empty(shape, dtype=torch.float32, device=f"cuda:{device}")
+        if len(shape) == 1:
+            t.normal_(1.0, 0.02, generator=g)
+        else:
+            t.normal_(0.0, 0.02 if name == "embed" else shape[1] ** -0.5, generator=g)
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        del t
+
+
+DESIGN_SIZES = {
+    # name: (layer-listed config, closest uniform preset, batch, prompt, decode steps)
+    "dense-1b": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 64, 512, 128),
+    "dense-1b-long": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256, share=2),
+                      "llama-3.2-1b", 16, 4096, 64),
+    "moe-1b": (lambda: dugopel_cfg(1024, 24, 16, 64, 32, 64, 96, 384, 512, 49155, moe=(32, 8, 8, 4)),
+               "granite-moe-1b", 128, 128, 128),
+}
+
+
+def design_bench(args):
+    """Prefill and decode throughput of the layer-listed design at sizes shaped like real models'
+    layers (random weights), beside the closest uniform model at equal width / depth / feed-forward
+    size, with the per-kernel-class device time of each and its fraction of the measured peaks."""
+    device = 0
+    peaks = load_peaks()
+    R = nvllm_pkg.sub("runner")
+    out = {"design": "dugopel", "dtype": "bf16", "data": "synthetic (random-init weights, random prompts)",
+           "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": {}}
+    names = [n for n in DESIGN_SIZES if args.design_size in (None, n)]
+    for name in names:
+        mk, base_name, batch, P, D = DESIGN_SIZES[name]
+        entry = {"batch": batch, "prompt_len": P, "decode_steps": D}
+        for which in ("dugopel", base_name):
+            cfg = mk() if which == "dugopel" else C.PRESETS[base_name]()
+            if which != "dugopel" and cfg.max_seq_len < P + D + 1:
+                from dataclasses import replace
+                cfg = replace(cfg, max_seq_len=P + D + 32)
+            job = Job(cfg, batch, P, D, 4321)
+            if which == "dugopel":
+                run = R.CudaModelRunner(cfg, dugopel_device_weights(cfg, device), precision=C.PREC_BF16,
+                                        num_kv_blocks=job.num_blocks, device=device, max_num_seqs=job.n,
+                                        max_batched_tokens=batch * P, sampling=None)
+            else:
+                run = make_runner(cfg, job, device, fast_weights=True)
+            run.set_speculation(False)
+            job.stage(run)
+            run.sync()
+            pre, dec = [], []
+            for it in range(args.warmup + args.steps):
+                run.timer_start()
+                run.rerun()
+                ms_p = run.timer_stop()
+                run.timer_start()
+                for _ in range(D):
+                    run.run_resident()
+                ms_d = run.timer_stop()
+                if it >= args.warmup:
+                    pre.append(ms_p)
+                    dec.append(ms_d)
+            run.set_profile(2)
+            run.rerun()
+            run.sync()
+            prof_p = run.get_profile()
+            run.set_profile(2)
+            for _ in range(D):
+                run.run_resident()
+            run.sync()
+            prof_d = run.get_profile()
+            run.set_profile(0)
+
+            def classes(prof, n_steps):
+                rows = {}
+                for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"]):
+                    if v["ms"] <= 0:
+                        continue
+                    r = {"ms_per_step": round(v["ms"] / n_steps, 4), "launches_per_step": v["launches"] // n_steps}
+                    if v["flops"] > 0 and v["flops"] / max(v["bytes"], 1.0) > 200:
+                        r["tflops"] = round(v["flops"] / v["ms"] / 1e9, 1)
+                        r["frac_of_measured_bf16"] = round(r["tflops"] / peaks["bf16_tflops_sustained"], 3)
+                    else:
+                        r["gbs"] = round(v["bytes"] / v["ms"] / 1e6, 1)
+                        r["frac_of_measured_hbm"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+                    rows[k] = r
+                return rows
+
+            mp, md = float(np.median(pre)), float(np.median(dec))
+            mem = run.memory_info()
+            entry[which] = {
+                "params_matmul_M": round(cfg.matmul_params() / 1e6, 1),
+                "cache_bytes_per_token": mem["kv"] // (job.num_blocks * 256),
+                "prefill_ms": round(mp, 3), "prefill_tok_s": round(batch * P / mp * 1e3),
+                "decode_us_per_step": round(md / D * 1e3, 1), "decode_tok_s": round(batch * D / md * 1e3),
+                "prefill_kernels": classes(prof_p, 1), "decode_kernels": classes(prof_d, D)}
+            run.close()
+        out["sizes"][name] = entry
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -470,7 +591,13 @@ def main():
     ap.add_argument("--no-profile", action="store_true")
     ap.add_argument("--no-tp", action="store_true",
                     help="skip the Falcon-7B tensor-parallel leg (configs[3] at tp = --gpus)")
+    ap.add_argument("--design", default=None, choices=["dugopel"],
+                    help="instead of the default workload: the layer-listed design beside the closest "
+                         "uniform model at equal size (prefill and decode, per-kernel roofline)")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES))
     args = ap.parse_args()
+    if args.design:
+        return design_bench(args)
 
     D = nvllm_pkg.sub("dist")
     rank, world, local_rank = D.env_ranks()

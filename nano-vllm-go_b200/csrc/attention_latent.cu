@@ -12,11 +12,13 @@
 //                         latent and rotates the shared key part into the pool row at slots[t],
 //                         and keeps sigmoid(W_g h) per head
 //  rope_table_kernel      cos / sin of pos * base^(-2i/dims) for the step's rows (double)
-//  latent_q_kernel        q = W_uq c_q (split-K partials) -> [q_n W_uk | rope(q_r)] per head
+//  latent_fold_*          at load: W_uk folded into the query up projection, W_uv into the output
+//                         projection (per head), so that both are plain GEMMs on the tensor cores
+//  latent_q_kernel        split-K sum of the folded query projection, rotation of q_r
 //  latent_attn_kernel     causal online-softmax attention of (query, head) items against the
 //                         latent rows; one warp per item, a CTA's items share each key tile;
 //                         optional key splits (decode) merged by latent_combine_kernel
-//  latent_out_kernel      head output = gate * W_uv (sum p c), written as the O projection's input
+//                         the head's sigmoid gate is applied where the sum is normalised
 // All arithmetic is fp32 (double for the angles); QT / KT are the activation / cache dtypes.
 #include <stdlib.h>
 
@@ -55,7 +57,8 @@ cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int 
 
 // ---------------------------------------------------------------- input-projection epilogue
 template <typename QT, typename KT>
-__global__ void __launch_bounds__(256) latent_prep_kernel(LatentArgs a) {
+__global__ void __launch_bounds__(256) latent_prep_kernel(LatentArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ float row[];  // [n_in]
   __shared__ float red[32];
@@ -102,81 +105,104 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(LatentArgs a) {
   }
   const float* g = row + a.q_rank + (a.own_kv ? a.R + a.rot : 0);
   for (int i = threadIdx.x; i < a.H; i += blockDim.x) a.gate[(size_t)t * a.H + i] = 1.0f / (1.0f + expf(-g[i]));
+  TRACE_EXIT(tr);
 }
 
 cudaError_t launch_latent_prep(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   const size_t smem = (size_t)(a.q_rank + a.R + a.rot + a.H) * sizeof(float);
   if (qdt == DT_F32 && kvdt == DT_F32)
-    (void)launch_k(latent_prep_kernel<float, float>, dim3(a.T), dim3(256), smem, st, a);
+    (void)launch_k(latent_prep_kernel<float, float>, dim3(a.T), dim3(256), smem, st, a, next_trace(20));
   else if (qdt == DT_BF16 && kvdt == DT_BF16)
-    (void)launch_k(latent_prep_kernel<bf16, bf16>, dim3(a.T), dim3(256), smem, st, a);
+    (void)launch_k(latent_prep_kernel<bf16, bf16>, dim3(a.T), dim3(256), smem, st, a, next_trace(20));
   else
     return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 
-// ---------------------------------------------------------------- absorbed query
-// CTA = (8 tokens, head).  The tokens' unrotated query parts sit in shared memory; thread r
-// walks the head's [dim][R] slice of W_uk (r contiguous: coalesced) and keeps 8 accumulators.
-constexpr int LQ_TT = 8;
-template <typename QT, typename WT>
-__global__ void __launch_bounds__(128) latent_q_kernel(LatentArgs a) {
+// ---------------------------------------------------------------- absorbed query, epilogue
+// The query up projection runs with the FOLDED weight (W_uk^T W_uq,n per head, then the rotated
+// rows of W_uq; latent_fold_q_kernel), so its output already is [q~ (R) | q_r (rot)] per head.
+// This kernel sums the split-K partials, rotates q_r and rounds to the activation dtype.
+template <typename QT>
+__global__ void __launch_bounds__(256) latent_q_kernel(LatentArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
   pdl_launch_dependents();
-  extern __shared__ float qs[];  // [LQ_TT][dim + rot]
-  const int t0 = blockIdx.x * LQ_TT, hd = blockIdx.y;
-  const int dq = a.dim + a.rot, Dk = a.R + a.rot;
-  const int nt = min(LQ_TT, a.T - t0);
+  const int t = blockIdx.x, Dk = a.R + a.rot, n = a.H * Dk, half = a.rot_dims / 2;
   pdl_wait();
-  for (int i = threadIdx.x; i < LQ_TT * dq; i += blockDim.x) {
-    const int tt = i / dq, d = i % dq;
-    float s = 0.f;
-    if (tt < nt)
-      for (int k = 0; k < a.q_S; k++)
-        s += a.q_p[(size_t)k * a.q_stride + (size_t)(t0 + tt) * a.q_ld + hd * dq + d];
-    qs[i] = s;
-  }
-  __syncthreads();
-  QT* out = (QT*)a.qabs;
-  const WT* W = (const WT*)a.w_uk + (size_t)hd * a.dim * a.R;
-  for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
-    float acc[LQ_TT];
-#pragma unroll
-    for (int tt = 0; tt < LQ_TT; tt++) acc[tt] = 0.f;
-    for (int d = 0; d < a.dim; d++) {
-      const float w = to_f32(W[(size_t)d * a.R + r]);
-#pragma unroll
-      for (int tt = 0; tt < LQ_TT; tt++) acc[tt] = fmaf(qs[tt * dq + d], w, acc[tt]);
+  QT* out = (QT*)a.qabs + (size_t)t * n;
+  const float* src = a.q_p + (size_t)t * a.q_ld;
+  const float* cs = a.cosT + (size_t)t * half;
+  const float* sn = a.sinT + (size_t)t * half;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int d = i % Dk - a.R;  // index inside the rotated part (negative: absorbed part)
+    float v = 0.f, pair = 0.f;
+    const int j = d < 0 || d >= a.rot_dims ? i : (d < half ? i + half : i - half);
+    for (int k = 0; k < a.q_S; k++) {
+      v += src[(size_t)k * a.q_stride + i];
+      if (j != i) pair += src[(size_t)k * a.q_stride + j];
     }
-#pragma unroll
-    for (int tt = 0; tt < LQ_TT; tt++)
-      if (tt < nt) out[((size_t)(t0 + tt) * a.H + hd) * Dk + r] = from_f32<QT>(acc[tt]);
+    if (j != i) v = d < half ? v * cs[d] - pair * sn[d] : v * cs[d - half] + pair * sn[d - half];
+    out[i] = from_f32<QT>(v);
   }
-  const int half = a.rot_dims / 2;
-  for (int i = threadIdx.x; i < nt * a.rot; i += blockDim.x) {
-    const int tt = i / a.rot, d = i % a.rot, t = t0 + tt;
-    const float* qr = qs + tt * dq + a.dim;
-    float o = qr[d];
-    if (d < half) {
-      o = qr[d] * a.cosT[(size_t)t * half + d] - qr[d + half] * a.sinT[(size_t)t * half + d];
-    } else if (d < a.rot_dims) {
-      const int j = d - half;
-      o = qr[d] * a.cosT[(size_t)t * half + j] + qr[j] * a.sinT[(size_t)t * half + j];
-    }
-    out[((size_t)t * a.H + hd) * Dk + a.R + d] = from_f32<QT>(o);
-  }
+  TRACE_EXIT(tr);
 }
 
-cudaError_t launch_latent_q(cudaStream_t st, int qdt, int wdt, const LatentArgs& a) {
+cudaError_t launch_latent_q(cudaStream_t st, int qdt, const LatentArgs& a) {
   if (a.T <= 0) return cudaSuccess;
-  dim3 grid(ceil_div(a.T, LQ_TT), a.H);
-  const size_t smem = (size_t)LQ_TT * (a.dim + a.rot) * sizeof(float);
-  if (qdt == DT_F32 && wdt == DT_F32)
-    (void)launch_k(latent_q_kernel<float, float>, grid, dim3(128), smem, st, a);
-  else if (qdt == DT_BF16 && wdt == DT_BF16)
-    (void)launch_k(latent_q_kernel<bf16, bf16>, grid, dim3(128), smem, st, a);
-  else
-    return cudaErrorInvalidValue;
+  if (qdt == DT_F32) (void)launch_k(latent_q_kernel<float>, dim3(a.T), dim3(256), 0, st, a, next_trace(21));
+  else (void)launch_k(latent_q_kernel<bf16>, dim3(a.T), dim3(256), 0, st, a, next_trace(21));
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- weight folding (once, at finalize)
+// wq[h * Dk + r, k]     = sum_d W_uk[h * dim + d, r] * W_uq[h * (dim + rot) + d, k]     r < R
+// wq[h * Dk + R + j, k] = W_uq[h * (dim + rot) + dim + j, k]
+// wo[n, h * R + r]      = sum_e W_o[n, h * vdim + e] * W_uv[h * vdim + e, r]
+// fp32 accumulation, one rounding to the weight dtype; the padding columns stay zero.
+template <typename WT>
+__global__ void latent_fold_q_kernel(const WT* __restrict__ w_uq, const WT* __restrict__ w_uk, WT* __restrict__ wq,
+                                     int H, int dim, int rot, int R, int q_rank, int ld) {
+  const int Dk = R + rot;
+  const size_t n = (size_t)H * Dk * q_rank;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int k = (int)(i % q_rank), row = (int)(i / q_rank), h = row / Dk, r = row % Dk;
+    float acc = 0.f;
+    if (r >= R) {
+      acc = to_f32(w_uq[((size_t)h * (dim + rot) + dim + (r - R)) * ld + k]);
+    } else {
+      for (int d = 0; d < dim; d++)
+        acc = fmaf(to_f32(w_uk[((size_t)h * dim + d) * R + r]), to_f32(w_uq[((size_t)h * (dim + rot) + d) * ld + k]), acc);
+    }
+    wq[(size_t)row * ld + k] = from_f32<WT>(acc);
+  }
+}
+template <typename WT>
+__global__ void latent_fold_o_kernel(const WT* __restrict__ w_o, const WT* __restrict__ w_uv, WT* __restrict__ wo,
+                                     int W, int H, int vdim, int R, int ld_o, int ld) {
+  const size_t n = (size_t)W * H * R;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ((size_t)H * R)), row = (int)(i / ((size_t)H * R)), h = c / R, r = c % R;
+    float acc = 0.f;
+    for (int e = 0; e < vdim; e++)
+      acc = fmaf(to_f32(w_o[(size_t)row * ld_o + h * vdim + e]), to_f32(w_uv[((size_t)h * vdim + e) * R + r]), acc);
+    wo[(size_t)row * ld + c] = from_f32<WT>(acc);
+  }
+}
+cudaError_t launch_latent_fold(cudaStream_t st, int wdt, const void* w_uq, const void* w_uk, void* wq, const void* w_o,
+                               const void* w_uv, void* wo, int W, int H, int dim, int rot, int vdim, int R,
+                               int q_rank, int q_rank_p, int ov_p, int ovr_p) {
+  if (wdt == DT_F32) {
+    latent_fold_q_kernel<float><<<148 * 8, 256, 0, st>>>((const float*)w_uq, (const float*)w_uk, (float*)wq, H, dim,
+                                                         rot, R, q_rank, q_rank_p);
+    latent_fold_o_kernel<float><<<148 * 8, 256, 0, st>>>((const float*)w_o, (const float*)w_uv, (float*)wo, W, H,
+                                                         vdim, R, ov_p, ovr_p);
+  } else {
+    latent_fold_q_kernel<bf16><<<148 * 8, 256, 0, st>>>((const bf16*)w_uq, (const bf16*)w_uk, (bf16*)wq, H, dim, rot,
+                                                        R, q_rank, q_rank_p);
+    latent_fold_o_kernel<bf16><<<148 * 8, 256, 0, st>>>((const bf16*)w_o, (const bf16*)w_uv, (bf16*)wo, W, H, vdim, R,
+                                                        ov_p, ovr_p);
+  }
   return cudaGetLastError();
 }
 
@@ -188,7 +214,8 @@ cudaError_t launch_latent_q(cudaStream_t st, int qdt, int wdt, const LatentArgs&
 // query broadcast from shared memory), the warp takes max / sum, and for the weighted sum lane i
 // owns latent entries i, i + 32, ... in registers.
 template <typename QT, typename KT>
-__global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs a) {
+__global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ float sm[];
   const int Dk = a.R + a.rot, ldk = Dk + 1;
@@ -204,7 +231,7 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
   const int start = a.tile_seq ? a.seq_start[seq] : a.seq_len[seq] - 1;  // decode steps advance seq_len only
   const int nq = min(a.qtile, n_new - q0);
   const int item0 = blockIdx.y * LAT_WARPS;
-  if (item0 >= nq * a.H) return;
+  if (item0 >= nq * a.H) return;  // nothing traced: an empty CTA
   const int item = item0 + warp;
   const bool valid = item < nq * a.H;
   const int qi = valid ? item / a.H : 0, head = valid ? item % a.H : 0;
@@ -270,15 +297,18 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
     }
     m = m_new;
   }
+  TRACE_EXIT(tr);
   if (!valid) return;
   if (gridDim.z == 1) {
-    const float inv = 1.0f / l;
-    QT* op = (QT*)a.olat + ((size_t)row * a.H + head) * a.R;
+    const float inv = a.gate[(size_t)row * a.H + head] / l;  // the head's sigmoid gate rides on the normalisation
+    QT* op = (QT*)a.olat + (size_t)row * a.o_ld + head * a.R;
 #pragma unroll
     for (int i = 0; i < LAT_NACC; i++) {
       const int r = i * 32 + lane;
       if (r < a.R) op[r] = from_f32<QT>(acc[i] * inv);
     }
+    if (head == a.H - 1)  // padding columns of the output projection's input
+      for (int r = a.H * a.R + lane; r < a.o_ld; r += 32) ((QT*)a.olat)[(size_t)row * a.o_ld + r] = from_f32<QT>(0.f);
   } else {
     // split record: [R] unnormalised sum, then m, l
     float* rec = a.split_ws + (((size_t)row * a.H + head) * gridDim.z + blockIdx.z) * (a.R + 2);
@@ -304,7 +334,8 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
 // layout; the P fragments come straight from the score accumulators.
 constexpr int LM_ROWS = 64, LM_KT = 64;
 template <int NR>
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int two_stage) {
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
+  TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t smem_lm[];
   const int Dk = a.R + a.rot, ld = Dk + 8, cpr = Dk / 8;
@@ -456,6 +487,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int 
     buf ^= 1;
   }
   cp_async_wait<0>();
+  TRACE_EXIT(tr);
 #pragma unroll
   for (int i = 0; i < 2; i++) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
@@ -467,12 +499,15 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int 
     if (item >= n_items) continue;
     const size_t it = (size_t)(row0 + q0) * a.H + item;  // row * H + head
     if (gridDim.z == 1) {
-      const float inv = 1.0f / l[i];
-      bf16* op = (bf16*)a.olat + it * a.R;
+      const int row = row0 + q0 + item / a.H, head = item % a.H;
+      const float inv = a.gate[it] / l[i];  // the head's sigmoid gate rides on the normalisation
+      bf16* op = (bf16*)a.olat + (size_t)row * a.o_ld + head * a.R;
 #pragma unroll
       for (int dn = 0; dn < NR; dn++)
         if (dn < nrt)
           *reinterpret_cast<uint32_t*>(op + dn * 8 + 2 * t) = pack_bf16(o[dn][2 * i] * inv, o[dn][2 * i + 1] * inv);
+      if (head == a.H - 1)  // padding columns of the output projection's input
+        for (int r = a.H * a.R + t; r < a.o_ld; r += 4) ((bf16*)a.olat)[(size_t)row * a.o_ld + r] = __float2bfloat16_rn(0.f);
     } else {
       float* rec = a.split_ws + (it * gridDim.z + blockIdx.z) * (a.R + 2);
 #pragma unroll
@@ -506,12 +541,13 @@ static cudaError_t launch_latent_mma(cudaStream_t st, const LatentArgs& a, int n
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(latent_attn_mma_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, LM_ROWS), ns);
-  (void)launch_k(latent_attn_mma_kernel<NR>, grid, dim3(128), smem, st, a, two);
+  (void)launch_k(latent_attn_mma_kernel<NR>, grid, dim3(128), smem, st, a, two, next_trace(22));
   return cudaGetLastError();
 }
 
 template <typename QT>
-__global__ void latent_combine_kernel(LatentArgs a, int n_splits) {
+__global__ void latent_combine_kernel(LatentArgs a, int n_splits, Trace tr) {
+  TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
   const size_t item = blockIdx.x;  // row * H + head
@@ -523,15 +559,22 @@ __global__ void latent_combine_kernel(LatentArgs a, int n_splits) {
     const float ms = rec[(size_t)s * (a.R + 2) + a.R];
     if (ms != -INFINITY) l += rec[(size_t)s * (a.R + 2) + a.R + 1] * expf(ms - m);
   }
-  QT* op = (QT*)a.olat + item * a.R;
+  const size_t row = item / a.H;
+  const int head = (int)(item % a.H);
+  QT* op = (QT*)a.olat + row * a.o_ld + head * a.R;
+  const float inv = a.gate[item] / l;
   for (int r = threadIdx.x; r < a.R; r += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < n_splits; s++) {
       const float ms = rec[(size_t)s * (a.R + 2) + a.R];
       if (ms != -INFINITY) o += rec[(size_t)s * (a.R + 2) + r] * expf(ms - m);
     }
-    op[r] = from_f32<QT>(o / l);
+    op[r] = from_f32<QT>(o * inv);
   }
+  if (head == a.H - 1)
+    for (int r = a.H * a.R + threadIdx.x; r < a.o_ld; r += blockDim.x)
+      ((QT*)a.olat)[row * a.o_ld + r] = from_f32<QT>(0.f);
+  TRACE_EXIT(tr);
 }
 
 int latent_attn_qtile() { return LAT_QTILE; }
@@ -539,7 +582,7 @@ int latent_attn_qtile() { return LAT_QTILE; }
 int latent_attn_splits(int n_seqs, int H, int max_len, int sm_count) {
   const int ctas = n_seqs * ceil_div(H, LAT_WARPS);
   int ns = ceil_div(2 * sm_count, ctas);
-  ns = min(ns, ceil_div(max_len, 8 * LAT_KT));  // at least 8 key tiles per split
+  ns = min(ns, ceil_div(max_len, 128));  // at least 128 keys per split
   return max(1, min(ns, 64));
 }
 
@@ -554,77 +597,22 @@ cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentA
     cudaError_t e = a.R <= 64 ? launch_latent_mma<8>(st, a, ns)
                     : a.R <= 128 ? launch_latent_mma<16>(st, a, ns) : launch_latent_mma<32>(st, a, ns);
     if (e != cudaSuccess) return e;
-    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns, next_trace(23));
     return cudaGetLastError();
   }
   if (qdt == DT_F32 && kvdt == DT_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(latent_attn_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(latent_attn_kernel<float, float>, grid, dim3(LAT_WARPS * 32), smem, st, a);
-    if (ns > 1) (void)launch_k(latent_combine_kernel<float>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+    (void)launch_k(latent_attn_kernel<float, float>, grid, dim3(LAT_WARPS * 32), smem, st, a, next_trace(22));
+    if (ns > 1) (void)launch_k(latent_combine_kernel<float>, dim3(a.T * a.H), dim3(64), 0, st, a, ns, next_trace(23));
   } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(latent_attn_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    (void)launch_k(latent_attn_kernel<bf16, bf16>, grid, dim3(LAT_WARPS * 32), smem, st, a);
-    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns);
+    (void)launch_k(latent_attn_kernel<bf16, bf16>, grid, dim3(LAT_WARPS * 32), smem, st, a, next_trace(22));
+    if (ns > 1) (void)launch_k(latent_combine_kernel<bf16>, dim3(a.T * a.H), dim3(64), 0, st, a, ns, next_trace(23));
   } else {
     return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
-}
-
-// ---------------------------------------------------------------- value expansion + head gate
-// out[t, h * vdim + e] = gate[t, h] * sum_r o[t, h, r] * W_uv[h * vdim + e, r]
-constexpr int LO_TT = 8;
-template <typename QT, typename WT>
-__global__ void __launch_bounds__(128) latent_out_kernel(LatentArgs a) {
-  pdl_launch_dependents();
-  extern __shared__ float os[];  // [LO_TT][R]
-  const int t0 = blockIdx.x * LO_TT, hd = blockIdx.y;
-  const int nt = min(LO_TT, a.T - t0);
-  pdl_wait();
-  const QT* o = (const QT*)a.olat;
-  for (int i = threadIdx.x; i < LO_TT * a.R; i += blockDim.x) {
-    const int tt = i / a.R, r = i % a.R;
-    os[i] = tt < nt ? to_f32(o[((size_t)(t0 + tt) * a.H + hd) * a.R + r]) : 0.f;
-  }
-  __syncthreads();
-  QT* out = (QT*)a.attn_out;
-  const WT* W = (const WT*)a.w_uv + (size_t)hd * a.vdim * a.R;
-  for (int e = threadIdx.x; e < a.vdim; e += blockDim.x) {
-    float acc[LO_TT];
-#pragma unroll
-    for (int tt = 0; tt < LO_TT; tt++) acc[tt] = 0.f;
-    const WT* wr = W + (size_t)e * a.R;
-    for (int r = 0; r < a.R; r++) {
-      const float w = to_f32(wr[r]);
-#pragma unroll
-      for (int tt = 0; tt < LO_TT; tt++) acc[tt] = fmaf(os[tt * a.R + r], w, acc[tt]);
-    }
-#pragma unroll
-    for (int tt = 0; tt < LO_TT; tt++)
-      if (tt < nt)
-        out[(size_t)(t0 + tt) * a.ov_p + hd * a.vdim + e] =
-            from_f32<QT>(acc[tt] * a.gate[(size_t)(t0 + tt) * a.H + hd]);
-  }
-  // zero the padding columns of the O projection's input once per token tile
-  if (hd == 0)
-    for (int i = threadIdx.x; i < nt * (a.ov_p - a.H * a.vdim); i += blockDim.x) {
-      const int pad = a.ov_p - a.H * a.vdim;
-      out[(size_t)(t0 + i / pad) * a.ov_p + a.H * a.vdim + i % pad] = from_f32<QT>(0.f);
-    }
-}
-
-cudaError_t launch_latent_out(cudaStream_t st, int qdt, int wdt, const LatentArgs& a) {
-  if (a.T <= 0) return cudaSuccess;
-  dim3 grid(ceil_div(a.T, LO_TT), a.H);
-  const size_t smem = (size_t)LO_TT * a.R * sizeof(float);
-  if (qdt == DT_F32 && wdt == DT_F32)
-    (void)launch_k(latent_out_kernel<float, float>, grid, dim3(128), smem, st, a);
-  else if (qdt == DT_BF16 && wdt == DT_BF16)
-    (void)launch_k(latent_out_kernel<bf16, bf16>, grid, dim3(128), smem, st, a);
-  else
-    return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

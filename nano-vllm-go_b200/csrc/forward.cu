@@ -101,7 +101,7 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     for (auto& y : h->ll) {
       cq = std::max(cq, (size_t)y.q_rank_p);
       heads = std::max(heads, (size_t)y.s.heads);
-      ol = std::max(ol, (size_t)y.s.heads * y.s.kv_rank);
+      ol = std::max(ol, (size_t)y.ovr_p);
     }
     WS(w.lat_cq, Tc * cq * asz);
     WS(w.lat_gate, Tc * heads * 4);

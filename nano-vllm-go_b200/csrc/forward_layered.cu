@@ -5,8 +5,9 @@
 // Every layer is a parallel block on the fp32 residual stream x:
 //     h = LayerNorm(x) (weight only);  x += mixer(h) + feed_forward(h)
 // Mixer "latent attention" (attention_latent.cu): one fused input projection [W_dq | W_dkv | W_g]
-// of h, RMS-normed latents, a query up projection, the absorbed-query attention over the paged
-// latent cache, value expansion + per-head sigmoid gate, output projection.  A layer with
+// of h, RMS-normed latents, the query up projection with W_uk folded in, the absorbed-query
+// attention over the paged latent cache (per-head sigmoid gate applied to its result), the output
+// projection with W_uv folded in.  A layer with
 // kv_from = j has no W_dkv and reads layer j's cache rows (written earlier in the same step).
 // Feed-forward: none, a dense clamped gated unit, or a group-limited top-k mixture of such
 // units (the routing runs inside the norm kernel, the expert GEMMs are the grouped ones the
@@ -28,7 +29,7 @@ void layered_free(nvllm_handle* h) {
     if (p) cudaFree(p);
   };
   for (auto& y : h->ll) {
-    F(y.norm_w); F(y.w_in); F(y.dq_norm); F(y.dkv_norm); F(y.w_uq); F(y.w_uk); F(y.w_uv); F(y.w_o);
+    F(y.norm_w); F(y.w_in); F(y.dq_norm); F(y.dkv_norm); F(y.w_uq); F(y.w_uk); F(y.w_uv); F(y.w_o); F(y.w_q); F(y.w_ov);
     F(y.w1); F(y.w2); F(y.router); F(y.moe_in); F(y.moe_out);
   }
   h->ll.clear();
@@ -164,6 +165,24 @@ int layered_finalize(nvllm_handle* h) {
   }
   for (auto& n : need)
     if (!got(n)) return set_err(h, NVLLM_ERR_INVALID, "missing tensor %s", n.c_str());
+  // fold the per-head key / value up projections into the query and output projections
+  // (attention_latent.cu), then drop the four tensors as loaded
+  for (int l = 0; l < h->L; l++) {
+    ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    cudaError_t e = launch_latent_fold(h->stream, h->wdt, y.w_uq, y.w_uk, y.w_q, y.w_o, y.w_uv, y.w_ov, h->H, s.heads,
+                                       s.dim, s.rot_dim, s.vdim, s.kv_rank, s.q_rank, y.q_rank_p, y.ov_p, y.ovr_p);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    if (e != cudaSuccess) return set_err(h, NVLLM_ERR_CUDA, "folding layer %d: %s", l, cudaGetErrorString(e));
+    const size_t wsz = dt_size(h->wdt);
+    const size_t freed = ((size_t)y.q_cols * y.q_rank_p + (size_t)s.heads * s.dim * s.kv_rank +
+                          (size_t)s.heads * s.vdim * s.kv_rank + (size_t)h->H * y.ov_p) * wsz;
+    for (void** p : {&y.w_uq, &y.w_uk, &y.w_uv, &y.w_o}) {
+      cudaFree(*p);
+      *p = nullptr;
+    }
+    h->weight_bytes -= std::min<uint64_t>(h->weight_bytes, freed);
+  }
   // cache pools: one per layer with its own down projection, rows [c | rotated key part]
   h->lat_pools.assign(h->L, nullptr);
   for (int l = 0; l < h->L; l++) {
@@ -229,7 +248,7 @@ int forward_step_layered(nvllm_handle* h) {
     const RopeTable& rt = h->ropes[y.rope];
     LatentArgs a{};
     a.T = T; a.H = s.heads; a.dim = s.dim; a.rot = s.rot_dim; a.rot_dims = s.rot_dims; a.vdim = s.vdim;
-    a.R = s.kv_rank; a.q_rank = s.q_rank; a.q_rank_p = y.q_rank_p; a.ov_p = y.ov_p; a.own_kv = own;
+    a.R = s.kv_rank; a.q_rank = s.q_rank; a.q_rank_p = y.q_rank_p; a.o_ld = y.ovr_p; a.own_kv = own;
     a.eps = h->cfg.norm_eps; a.scale = s.scale;
     a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
     a.dq_norm = y.dq_norm; a.dkv_norm = y.dkv_norm;
@@ -237,10 +256,10 @@ int forward_step_layered(nvllm_handle* h) {
     a.slots = d + L.slots;
     a.pool = h->lat_pools[y.pool];
     a.cq = w.lat_cq; a.gate = w.lat_gate;
-    a.w_uk = y.w_uk; a.qabs = w.q;
+    a.qabs = w.q;
     a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
     a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
-    a.olat = w.lat_o; a.w_uv = y.w_uv; a.attn_out = w.attn_out;
+    a.olat = w.lat_o;
     a.split_ws = w.attn_ws;
     if (L.prefill) {
       a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles;
@@ -255,34 +274,26 @@ int forward_step_layered(nvllm_handle* h) {
                    (double)T * y.n_in * 4 * (pin.S - 1));
       LAUNCH(h, launch_latent_prep(st, h->adt, h->kvdt, a));
     }
+    const int qn = s.heads * y.Dk;
     Pending pq;
-    if ((rc = run_gemm(h, w.lat_cq, y.q_rank_p, y.w_uq, T, y.q_cols, y.q_rank_p, 1.f, w.ws_a, w.ws_a_floats,
-                       y.q_cols, &pq)))
+    if ((rc = run_gemm(h, w.lat_cq, y.q_rank_p, y.w_q, T, qn, y.q_rank_p, 1.f, w.ws_a, w.ws_a_floats, qn, &pq)))
       return rc;
-    a.q_p = pq.p; a.q_S = pq.S; a.q_stride = pq.stride; a.q_ld = y.q_cols;
+    a.q_p = pq.p; a.q_S = pq.S; a.q_stride = pq.stride; a.q_ld = qn;
     {
-      ProfScope ps(h, NVLLM_K_ROPE_KV, (double)T * y.q_cols * 4 + (double)T * s.heads * y.Dk * asz +
-                                           (double)s.heads * s.dim * s.kv_rank * wsz,
-                   2.0 * T * s.heads * s.dim * s.kv_rank, (double)T * y.q_cols * 4 * (pq.S - 1));
-      LAUNCH(h, launch_latent_q(st, h->adt, h->wdt, a));
+      ProfScope ps(h, NVLLM_K_ROPE_KV, (double)T * qn * (4 + asz), 0, (double)T * qn * 4 * (pq.S - 1));
+      LAUNCH(h, launch_latent_q(st, h->adt, a));
     }
     {
       // algorithmic: every cached row of the contexts once; flops: scores over Dk, sums over R
       const double bytes = (double)L.sum_len * y.Dk * kvsz;
       const double flops = 2.0 * s.heads * (y.Dk + s.kv_rank) * L.attn_pairs;
       ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE, bytes, flops,
-                   (double)T * s.heads * (y.Dk + s.kv_rank) * asz);
+                   (double)T * (qn + y.ovr_p) * asz);
       LAUNCH(h, launch_latent_attn(st, h->adt, h->kvdt, a));
       if (a.n_splits > 1) h->launches++;
     }
-    {
-      ProfScope ps(h, NVLLM_K_MISC, (double)T * (s.heads * s.kv_rank + y.ov_p) * asz +
-                                        (double)s.heads * s.vdim * s.kv_rank * wsz,
-                   2.0 * T * s.heads * s.vdim * s.kv_rank);
-      LAUNCH(h, launch_latent_out(st, h->adt, h->wdt, a));
-    }
     Pending pa;
-    if ((rc = run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, &pa))) return rc;
+    if ((rc = run_gemm(h, w.lat_o, y.ovr_p, y.w_ov, T, H, y.ovr_p, 1.f, w.ws_b, w.ws_b_floats, H, &pa))) return rc;
     // ---- feed-forward on the same normed input
     Pending pm;
     if (s.mlp == NVLLM_MLP_DENSE) {
@@ -292,12 +303,23 @@ int forward_step_layered(nvllm_handle* h) {
                     w.hbuf, s.ff, nullptr);
       h->glu_limit_cur = 0.f;
       if (rc) return rc;
-      if (h1.S > 0) {
-        ProfScope ps(h, NVLLM_K_ACT, (double)T * 2 * s.ff * 4 + (double)T * s.ff * asz, 0,
-                     (double)T * 2 * s.ff * 4 * (h1.S - 1));
-        LAUNCH(h, launch_act(st, h->adt, T, s.ff, h1.p, h1.S, h1.stride, nullptr, 1, w.hbuf, s.limit));
+      // steps of <= 8 rows: the gated unit is built inside the down projection's GEMV (one launch less)
+      const char* gpre_env = getenv("NVLLM_GEMV_PRE");
+      if (h1.S > 0 && T <= 8 && !(gpre_env && atoi(gpre_env) == 0)) {
+        GemvPre ga{};
+        ga.mode = 2; ga.hp = h1.p; ga.Sh = h1.S; ga.hstride = h1.stride; ga.hld = 2 * s.ff;
+        ga.swiglu = 1; ga.glu_limit = s.limit;
+        if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm, 0, nullptr, 0,
+                           nullptr, nullptr, 0, 0.0, nullptr, nullptr, &ga)))
+          return rc;
+      } else {
+        if (h1.S > 0) {
+          ProfScope ps(h, NVLLM_K_ACT, (double)T * 2 * s.ff * 4 + (double)T * s.ff * asz, 0,
+                       (double)T * 2 * s.ff * 4 * (h1.S - 1));
+          LAUNCH(h, launch_act(st, h->adt, T, s.ff, h1.p, h1.S, h1.stride, nullptr, 1, w.hbuf, s.limit));
+        }
+        if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
       }
-      if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
     } else if (s.mlp == NVLLM_MLP_MOE) {
       if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, s.ff, s.limit, y.moe_in, y.moe_out, &pm))) return rc;
     }
@@ -407,8 +429,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   h->parallel = true;
   h->num_blocks = g.num_kv_blocks;
   h->logit_softcap = c->logit_softcap;
-  h->graphs_enabled = 0;  // step graphs and the speculative step are keyed on the uniform models' shapes
-  h->spec_enabled = 0;
+  h->spec_enabled = 0;  // the speculative next step is keyed on the uniform models' shapes
   if (const char* env = getenv("NVLLM_SKIP")) h->skip_mask = (unsigned)strtoul(env, nullptr, 0);
   auto fail = [&](cudaError_t ce, const char* what) {
     int code = (ce == cudaErrorMemoryAllocation) ? NVLLM_ERR_NOMEM : NVLLM_ERR_CUDA;
@@ -446,6 +467,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     y.q_cols = s.heads * (s.dim + s.rot_dim);
     y.q_rank_p = (int)up8(s.q_rank);
     y.ov_p = (int)up8((size_t)s.heads * s.vdim);
+    y.ovr_p = (int)up8((size_t)s.heads * s.kv_rank);
     y.pool = s.kv_from < 0 ? l : s.kv_from;
     for (size_t r = 0; r < h->ropes.size(); r++)
       if (h->ropes[r].base == (double)s.rot_base && h->ropes[r].dims == s.rot_dims) y.rope = (int)r;
@@ -464,6 +486,8 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     AL(y.w_uk, (size_t)s.heads * s.dim * s.kv_rank * wsz);
     AL(y.w_uv, (size_t)s.heads * s.vdim * s.kv_rank * wsz);
     AL(y.w_o, (size_t)W * y.ov_p * wsz);
+    AL(y.w_q, (size_t)s.heads * y.Dk * y.q_rank_p * wsz);
+    AL(y.w_ov, (size_t)W * y.ovr_p * wsz);
     if (s.mlp == NVLLM_MLP_DENSE) {
       AL(y.w1, (size_t)2 * s.ff * W * wsz);
       AL(y.w2, (size_t)W * s.ff * wsz);
@@ -479,8 +503,8 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       h->F = std::max(h->F, s.ff);
     }
     // extents the shared workspace is sized by (forward.cu ensure_workspace)
-    qkv_cols = std::max(qkv_cols, std::max(y.n_in, y.q_cols));
-    q_cols = std::max(q_cols, std::max(s.heads * y.Dk, y.ov_p));
+    qkv_cols = std::max(qkv_cols, std::max(y.n_in, s.heads * y.Dk));
+    q_cols = std::max(q_cols, s.heads * y.Dk);
     h->nh = std::max(h->nh, s.heads);
     h->hd = std::max(h->hd, s.kv_rank);
   }

@@ -41,13 +41,16 @@ struct ListedLayer {
   int n_in = 0;      // rows of the fused input projection [dq | dkv (own cache only) | g]
   int q_cols = 0;    // heads * (dim + rot_dim)
   int q_rank_p = 0;  // q_rank rounded up to 8 (K of the query up projection)
-  int ov_p = 0;      // heads * vdim rounded up to 8 (K of the output projection)
+  int ov_p = 0;      // heads * vdim rounded up to 8 (row stride of W_o as loaded)
+  int ovr_p = 0;     // heads * kv_rank rounded up to 8 (K of the folded output projection)
   int pool = -1;     // index of the cache pool this layer reads (its own, or its source layer's)
   int rope = -1;     // index of its rotation table
   float* norm_w = nullptr;
   void* w_in = nullptr;
   float *dq_norm = nullptr, *dkv_norm = nullptr;
-  void *w_uq = nullptr, *w_uk = nullptr, *w_uv = nullptr, *w_o = nullptr;
+  void *w_uq = nullptr, *w_uk = nullptr, *w_uv = nullptr, *w_o = nullptr;  // as loaded; freed once folded
+  void* w_q = nullptr;   // [heads * Dk, q_rank_p]: per head W_uk^T W_uq,n (kv_rank rows), then W_uq's rotated rows
+  void* w_ov = nullptr;  // [W, ovr_p]: per head W_o,h W_uv,h
   void *w1 = nullptr, *w2 = nullptr;  // dense feed-forward: [2 ff, W] gate / up interleaved, [W, ff]
   float* router = nullptr;            // [experts, W] fp32
   void *moe_in = nullptr, *moe_out = nullptr;  // [experts, 2 ff, W] interleaved, [experts, W, ff]
@@ -114,7 +117,7 @@ struct Workspace {
   // latent attention (forward_layered.cu)
   void* lat_cq = nullptr;     // [T, max q_rank_p] act dtype
   float* lat_gate = nullptr;  // [T, max heads]
-  void* lat_o = nullptr;      // [T, max heads * kv_rank] act dtype
+  void* lat_o = nullptr;      // [T, max ovr_p] act dtype
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order

@@ -353,7 +353,8 @@ cudaError_t launch_attn_decode_t(cudaStream_t st, const AttnArgs& a);
 // buffers of its four kernels.
 constexpr int LAT_QTILE = 16;  // new tokens per attention tile (the host builds the tile list)
 struct LatentArgs {
-  int T, H, dim, rot, rot_dims, vdim, R, q_rank, q_rank_p, ov_p;
+  int T, H, dim, rot, rot_dims, vdim, R, q_rank, q_rank_p;
+  int o_ld;              // row stride of olat: heads * R rounded up to 8 (padding written as zeros)
   int own_kv;            // the layer has its own key/value down projection (writes the pool)
   float eps, scale;
   // fused input projection [dq | dkv | g]: split-K partials [S][T][in_ld]
@@ -364,28 +365,28 @@ struct LatentArgs {
   void* pool;                        // [blocks * 256][R + rot] cache dtype
   void* cq;                          // [T, q_rank_p] act dtype (zero padded)
   float* gate;                       // [T, H] sigmoid of the head gates
-  // query up projection partials [S][T][q_ld], W_uk [H * dim, R], absorbed queries [T, H, R + rot]
+  // folded query projection partials [S][T][q_ld] -> absorbed queries [T, H, R + rot] act dtype
   const float* q_p; int q_S; size_t q_stride; int q_ld;
-  const void* w_uk;
   void* qabs;
   // attention
   const int* block_tables; int max_blocks;
   const int *cu_q, *seq_start, *seq_len, *tile_seq, *tile_q0;  // without a tile list: one new token per sequence at seq_len - 1
   int n_tiles, qtile, n_splits;
   float* split_ws;                   // [T, H, n_splits, R + 2]
-  void* olat;                        // [T, H, R] act dtype
-  // output
-  const void* w_uv;                  // [H * vdim, R]
-  void* attn_out;                    // [T, ov_p] act dtype
+  void* olat;                        // [T, o_ld] act dtype: gate * sum p c per head = input of the folded output projection
 };
 cudaError_t launch_rope_table(cudaStream_t st, const int* positions, int T, int half,
                               const double* inv_freq, float* cosT, float* sinT);
 cudaError_t launch_latent_prep(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a);
-cudaError_t launch_latent_q(cudaStream_t st, int qdt, int wdt, const LatentArgs& a);
+cudaError_t launch_latent_q(cudaStream_t st, int qdt, const LatentArgs& a);
+// once per layer at finalize: wq [H (R + rot), q_rank_p] and wo [W, ovr_p] from the four checkpoint
+// tensors (W_uq [H (dim + rot), q_rank_p], W_uk [H dim, R], W_o [W, ov_p], W_uv [H vdim, R])
+cudaError_t launch_latent_fold(cudaStream_t st, int wdt, const void* w_uq, const void* w_uk, void* wq, const void* w_o,
+                               const void* w_uv, void* wo, int W, int H, int dim, int rot, int vdim, int R,
+                               int q_rank, int q_rank_p, int ov_p, int ovr_p);
 int latent_attn_qtile();
 int latent_attn_splits(int n_seqs, int H, int max_len, int sm_count);
 cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a);
-cudaError_t launch_latent_out(cudaStream_t st, int qdt, int wdt, const LatentArgs& a);
 // out[i] = cap * tanh(sum_s p[s * stride + i] / cap)   (cap <= 0: plain sum)
 cudaError_t launch_softcap(cudaStream_t st, const float* p, int S, size_t stride, size_t n, float cap,
                            float* out);

@@ -99,8 +99,12 @@ static int graphed_step(nvllm_handle* h, int slot, Pre pre, bool* used) {
   sig.d = L.d;
   sig.n = L.n;
   sig.max_blocks = L.max_blocks;
-  sig.n_splits = attn_decode_splits(h->adt, h->kvdt, L.n, h->nh, h->nkv, h->hd, L.max_len,
-                                    h->sm_count);
+  if (h->layered) {
+    // every layer picks its own key split from (batch, its heads, longest context)
+    for (auto& y : h->ll) sig.n_splits += latent_attn_splits(L.n, y.s.heads, L.max_len, h->sm_count);
+  } else {
+    sig.n_splits = attn_decode_splits(h->adt, h->kvdt, L.n, h->nh, h->nkv, h->hd, L.max_len, h->sm_count);
+  }
   if (!h->step_graph[slot] || !(sig == h->graph_sig[slot])) {
     if (h->step_graph[slot]) cudaGraphExecDestroy(h->step_graph[slot]);
     h->step_graph[slot] = nullptr;
