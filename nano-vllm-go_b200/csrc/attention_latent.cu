@@ -65,10 +65,19 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(LatentArgs a, Trace tr
   const int t = blockIdx.x;
   const int n_in = a.q_rank + (a.own_kv ? a.R + a.rot : 0) + a.H;
   pdl_wait();
-  for (int i = threadIdx.x; i < n_in; i += blockDim.x) {
-    float s = 0.f;
-    for (int k = 0; k < a.in_S; k++) s += a.in_p[(size_t)k * a.in_stride + (size_t)t * a.in_ld + i];
-    row[i] = s;
+  if ((n_in & 7) == 0 && (a.in_stride & 7) == 0) {
+    for (int i = threadIdx.x * 8; i < n_in; i += blockDim.x * 8) {
+      float v[8];
+      sum_partials8(a.in_p + (size_t)t * a.in_ld + i, a.in_S, a.in_stride, v);
+#pragma unroll
+      for (int j = 0; j < 8; j++) row[i + j] = v[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < n_in; i += blockDim.x) {
+      float s = 0.f;
+      for (int k = 0; k < a.in_S; k++) s += a.in_p[(size_t)k * a.in_stride + (size_t)t * a.in_ld + i];
+      row[i] = s;
+    }
   }
   __syncthreads();
   // query latent: c_q = v / sqrt(mean(v^2) + eps) * w
@@ -134,7 +143,19 @@ __global__ void __launch_bounds__(256) latent_q_kernel(LatentArgs a, Trace tr) {
   const float* src = a.q_p + (size_t)t * a.q_ld;
   const float* cs = a.cosT + (size_t)t * half;
   const float* sn = a.sinT + (size_t)t * half;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  // absorbed part, 8 entries at a time when the sizes allow (sum of the slices, one rounding)
+  const bool vec = (a.R & 7) == 0 && (Dk & 7) == 0 && (a.q_stride & 7) == 0 && (a.q_ld & 7) == 0;
+  if (vec) {
+    const int vph = a.R / 8;  // vectors per head
+    for (int v = threadIdx.x; v < a.H * vph; v += blockDim.x) {
+      const int i = (v / vph) * Dk + (v % vph) * 8;
+      float acc[8];
+      sum_partials8(src + i, a.q_S, a.q_stride, acc);
+      store8(out + i, acc);
+    }
+  }
+  for (int i0 = threadIdx.x; i0 < (vec ? a.H * a.rot : n); i0 += blockDim.x) {
+    const int i = vec ? (i0 / a.rot) * Dk + a.R + i0 % a.rot : i0;
     const int d = i % Dk - a.R;  // index inside the rotated part (negative: absorbed part)
     float v = 0.f, pair = 0.f;
     const int j = d < 0 || d >= a.rot_dims ? i : (d < half ? i + half : i - half);
@@ -332,9 +353,9 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
 // S = Q K^T over all Dk columns; the weighted sum P V takes the first R columns of the SAME tile
 // (ldmatrix.trans), so a cached row is staged once for both.  Online softmax in the accumulator
 // layout; the P fragments come straight from the score accumulators.
-constexpr int LM_ROWS = 64, LM_KT = 64;
-template <int NR>
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
+constexpr int LM_KT = 64;
+template <int NR, int LM_ROWS>
+__global__ void __launch_bounds__(LM_ROWS * 2) latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t smem_lm[];
@@ -532,17 +553,23 @@ static bool latent_mma_ok(int qdt, int kvdt, const LatentArgs& a) {
   return latent_mma_enabled() && qdt == DT_BF16 && kvdt == DT_BF16 && ((a.R + a.rot) % 16) == 0 && (a.R % 16) == 0 &&
          a.R <= 256 && a.scale > 0.f;
 }
+template <int NR, int ROWS>
+static cudaError_t launch_latent_mma_r(cudaStream_t st, const LatentArgs& a, int ns) {
+  const int Dk = a.R + a.rot;
+  const size_t one = (size_t)LM_KT * (Dk + 8) * 2, qb = (size_t)ROWS * (Dk + 8) * 2;
+  const int two = qb + 2 * one <= 200 * 1024 ? 1 : 0;
+  const size_t smem = qb + one * (two ? 2 : 1);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NR, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, ROWS), ns);
+  (void)launch_k(latent_attn_mma_kernel<NR, ROWS>, grid, dim3(ROWS * 2), smem, st, a, two, next_trace(22));
+  return cudaGetLastError();
+}
+// 128 items per CTA (8 warps) when a tile has that many: each staged key tile then serves twice the rows
 template <int NR>
 static cudaError_t launch_latent_mma(cudaStream_t st, const LatentArgs& a, int ns) {
-  const int Dk = a.R + a.rot;
-  const size_t one = (size_t)LM_KT * (Dk + 8) * 2;
-  const int two = 3 * one <= 200 * 1024 ? 1 : 0;
-  const size_t smem = one * (two ? 3 : 2);
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(latent_attn_mma_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, LM_ROWS), ns);
-  (void)launch_k(latent_attn_mma_kernel<NR>, grid, dim3(128), smem, st, a, two, next_trace(22));
-  return cudaGetLastError();
+  if (NR <= 16 && a.qtile * a.H >= 128) return launch_latent_mma_r<NR, 128>(st, a, ns);
+  return launch_latent_mma_r<NR, 64>(st, a, ns);
 }
 
 template <typename QT>
@@ -580,10 +607,14 @@ __global__ void latent_combine_kernel(LatentArgs a, int n_splits, Trace tr) {
 int latent_attn_qtile() { return LAT_QTILE; }
 
 int latent_attn_splits(int n_seqs, int H, int max_len, int sm_count) {
-  const int ctas = n_seqs * ceil_div(H, LAT_WARPS);
-  int ns = ceil_div(2 * sm_count, ctas);
-  ns = min(ns, ceil_div(max_len, 128));  // at least 128 keys per split
-  return max(1, min(ns, 64));
+  static const int forced = getenv("NVLLM_LATENT_SPLITS") ? atoi(getenv("NVLLM_LATENT_SPLITS")) : 0;
+  if (forced > 0) return min(forced, 64);
+  // decode is latency-bound per key tile (a cached row is a few hundred bytes for all heads):
+  // about three 64-key tiles per split, as long as all CTAs of the step stay resident
+  const int ctas = n_seqs * ceil_div(H, 64);
+  int ns = ceil_div(ceil_div(max_len, 64), 3);
+  ns = min(ns, max(1, 4 * sm_count / max(1, ctas)));
+  return max(1, min(ns, 32));
 }
 
 cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentArgs& a) {
