@@ -463,12 +463,12 @@ def dugopel_cfg(width, n_layers, heads, dim, rot_dim, vdim, kv_rank, q_rank, ff,
                   kv_from=(l - l % share) if share and l % share else -1)
         if moe and l > 0:
             kw.update(mlp=C.MLP_MOE, ff=ff, limit=7.0, experts=moe[0], top=moe[1], groups=moe[2],
-                      keep_groups=moe[3], router_scale=2.5)
+                      keep_groups=moe[3], router_scale=1.5)
         else:
             kw.update(mlp=C.MLP_DENSE, ff=ff if not moe else ff * moe[1], limit=7.0)
         layers.append(C.LayerSpec(**kw))
     return C.ListedModelConfig("dugopel", vocab, width, tuple(layers), 1e-5, embedding_scale=1.0,
-                               logit_softcap=30.0)
+                               logit_softcap=50.0)
 
 
 def dugopel_device_weights(cfg, device, seed=1234):

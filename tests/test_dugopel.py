@@ -125,7 +125,7 @@ def tol(prec):
 
 def check(got, want, prec, what=""):
     """fp32: every row within 2e-4 of the largest logit.  bf16: rounding of the residual stream
-    can flip a close expert choice at a single position (no fault: the design router is fp32 on a
+    can flip a close expert choice at a single position (no fault: the design's router is fp32 on a
     bf16-rounded input), so up to one row in sixteen may be off by more — but never grossly."""
     want = np.asarray(want).reshape(-1, np.asarray(want).shape[-1])
     got = np.asarray(got).reshape(want.shape)
