@@ -100,7 +100,7 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
     else if (rest == "mix.o") mat(y.w_o, W, (int64_t)s.heads * s.vdim, y.ov_p);
     else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.gate") mat(y.w1, s.ff, W, W, 0, 2, 0);
     else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.up") mat(y.w1, s.ff, W, W, 0, 2, 1);
-    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.down") mat(y.w2, W, s.ff, s.ff);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.down") mat(y.w2, W, s.ff, y.ff_p);
     else if (s.mlp == NVLLM_MLP_MOE && rest == "mlp.router") {
       mat(y.router, s.experts, W, W);
       d.ddt = DT_F32;
@@ -111,9 +111,9 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
       while (i < rest.size() && rest[i] >= '0' && rest[i] <= '9') e = e * 10 + (rest[i++] - '0');
       const std::string part = i < rest.size() ? rest.substr(i) : "";
       if (i == 5 || e >= s.experts) return set_err(h, NVLLM_ERR_INVALID, "unknown tensor %s", cname);
-      if (part == ".gate") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * s.ff, 2, 0);
-      else if (part == ".up") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * s.ff, 2, 1);
-      else if (part == ".down") mat(y.moe_out, W, s.ff, s.ff, (size_t)e * W);
+      if (part == ".gate") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * y.ff_p, 2, 0);
+      else if (part == ".up") mat(y.moe_in, s.ff, W, W, (size_t)e * 2 * y.ff_p, 2, 1);
+      else if (part == ".down") mat(y.moe_out, W, s.ff, y.ff_p, (size_t)e * W);
     }
   }
   if (!d.p) return set_err(h, NVLLM_ERR_INVALID, "tensor %s does not belong to this model", cname);
@@ -297,31 +297,32 @@ int forward_step_layered(nvllm_handle* h) {
     // ---- feed-forward on the same normed input
     Pending pm;
     if (s.mlp == NVLLM_MLP_DENSE) {
+      const int ff = y.ff_p;  // padded with zero rows / columns: the gated unit of (0, 0) is 0
       Pending h1;
       h->glu_limit_cur = s.limit;
-      rc = run_gemm(h, w.xn, H, y.w1, T, 2 * s.ff, H, 1.f, w.ws_a, w.ws_a_floats, 2 * s.ff, &h1, TC5_EPI_SWIGLU,
-                    w.hbuf, s.ff, nullptr);
+      rc = run_gemm(h, w.xn, H, y.w1, T, 2 * ff, H, 1.f, w.ws_a, w.ws_a_floats, 2 * ff, &h1, TC5_EPI_SWIGLU,
+                    w.hbuf, ff, nullptr);
       h->glu_limit_cur = 0.f;
       if (rc) return rc;
       // steps of <= 8 rows: the gated unit is built inside the down projection's GEMV (one launch less)
       const char* gpre_env = getenv("NVLLM_GEMV_PRE");
       if (h1.S > 0 && T <= 8 && !(gpre_env && atoi(gpre_env) == 0)) {
         GemvPre ga{};
-        ga.mode = 2; ga.hp = h1.p; ga.Sh = h1.S; ga.hstride = h1.stride; ga.hld = 2 * s.ff;
+        ga.mode = 2; ga.hp = h1.p; ga.Sh = h1.S; ga.hstride = h1.stride; ga.hld = 2 * ff;
         ga.swiglu = 1; ga.glu_limit = s.limit;
-        if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm, 0, nullptr, 0,
+        if ((rc = run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm, 0, nullptr, 0,
                            nullptr, nullptr, 0, 0.0, nullptr, nullptr, &ga)))
           return rc;
       } else {
         if (h1.S > 0) {
-          ProfScope ps(h, NVLLM_K_ACT, (double)T * 2 * s.ff * 4 + (double)T * s.ff * asz, 0,
-                       (double)T * 2 * s.ff * 4 * (h1.S - 1));
-          LAUNCH(h, launch_act(st, h->adt, T, s.ff, h1.p, h1.S, h1.stride, nullptr, 1, w.hbuf, s.limit));
+          ProfScope ps(h, NVLLM_K_ACT, (double)T * 2 * ff * 4 + (double)T * ff * asz, 0,
+                       (double)T * 2 * ff * 4 * (h1.S - 1));
+          LAUNCH(h, launch_act(st, h->adt, T, ff, h1.p, h1.S, h1.stride, nullptr, 1, w.hbuf, s.limit));
         }
-        if ((rc = run_gemm(h, w.hbuf, s.ff, y.w2, T, H, s.ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
+        if ((rc = run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
       }
     } else if (s.mlp == NVLLM_MLP_MOE) {
-      if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, s.ff, s.limit, y.moe_in, y.moe_out, &pm))) return rc;
+      if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, y.ff_p, s.limit, y.moe_in, y.moe_out, &pm))) return rc;
     }
     if (pm.p) {
       p1 = pm;  // the expert combine can only be the first addend of the norm kernel
@@ -385,7 +386,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       if (j.kv_rank != s.kv_rank || j.rot_dim != s.rot_dim) return bad(l, "kv_from layer has other cache sizes");
     }
     if (s.mlp < NVLLM_MLP_NONE || s.mlp > NVLLM_MLP_MOE) return bad(l, "unknown feed-forward kind");
-    if (s.mlp != NVLLM_MLP_NONE && (s.ff <= 0 || s.ff % 8)) return bad(l, "ff must be a positive multiple of 8");
+    if (s.mlp != NVLLM_MLP_NONE && s.ff <= 0) return bad(l, "ff must be positive");
     if (s.mlp != NVLLM_MLP_NONE && !(s.limit > 0.f)) return bad(l, "limit must be positive");
     if (s.mlp == NVLLM_MLP_MOE) {
       if (s.experts <= 0 || s.experts > 256 || s.top <= 0 || s.top > 32 || s.top > s.experts)
@@ -468,6 +469,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     y.q_rank_p = (int)up8(s.q_rank);
     y.ov_p = (int)up8((size_t)s.heads * s.vdim);
     y.ovr_p = (int)up8((size_t)s.heads * s.kv_rank);
+    y.ff_p = (int)up8((size_t)std::max(s.ff, 0));
     y.pool = s.kv_from < 0 ? l : s.kv_from;
     for (size_t r = 0; r < h->ropes.size(); r++)
       if (h->ropes[r].base == (double)s.rot_base && h->ropes[r].dims == s.rot_dims) y.rope = (int)r;
@@ -489,18 +491,18 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     AL(y.w_q, (size_t)s.heads * y.Dk * y.q_rank_p * wsz);
     AL(y.w_ov, (size_t)W * y.ovr_p * wsz);
     if (s.mlp == NVLLM_MLP_DENSE) {
-      AL(y.w1, (size_t)2 * s.ff * W * wsz);
-      AL(y.w2, (size_t)W * s.ff * wsz);
-      qkv_cols = std::max(qkv_cols, 2 * s.ff);
-      h->F = std::max(h->F, s.ff);
+      AL(y.w1, (size_t)2 * y.ff_p * W * wsz);
+      AL(y.w2, (size_t)W * y.ff_p * wsz);
+      qkv_cols = std::max(qkv_cols, 2 * y.ff_p);
+      h->F = std::max(h->F, y.ff_p);
     } else if (s.mlp == NVLLM_MLP_MOE) {
       AL(y.router, (size_t)s.experts * W * 4);
-      AL(y.moe_in, (size_t)s.experts * 2 * s.ff * W * wsz);
-      AL(y.moe_out, (size_t)s.experts * W * s.ff * wsz);
+      AL(y.moe_in, (size_t)s.experts * 2 * y.ff_p * W * wsz);
+      AL(y.moe_out, (size_t)s.experts * W * y.ff_p * wsz);
       h->moe = true;
       h->E = std::max(h->E, s.experts);
       h->topk = std::max(h->topk, s.top);
-      h->F = std::max(h->F, s.ff);
+      h->F = std::max(h->F, y.ff_p);
     }
     // extents the shared workspace is sized by (forward.cu ensure_workspace)
     qkv_cols = std::max(qkv_cols, std::max(y.n_in, s.heads * y.Dk));

@@ -43,6 +43,7 @@ struct ListedLayer {
   int q_rank_p = 0;  // q_rank rounded up to 8 (K of the query up projection)
   int ov_p = 0;      // heads * vdim rounded up to 8 (row stride of W_o as loaded)
   int ovr_p = 0;     // heads * kv_rank rounded up to 8 (K of the folded output projection)
+  int ff_p = 0;      // ff rounded up to 8 (zero rows / columns: they contribute nothing)
   int pool = -1;     // index of the cache pool this layer reads (its own, or its source layer's)
   int rope = -1;     // index of its rotation table
   float* norm_w = nullptr;

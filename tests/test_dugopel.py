@@ -56,6 +56,14 @@ def mixed_model(**kw):
                   layer(mixer(heads=5, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=40), dense(ff=24, limit=0.7))], **kw)
 
 
+def odd_model():
+    """Sizes that are multiples of nothing convenient: no vector or tensor-core path may be assumed."""
+    m = dict(heads=3, dim=12, rot_dim=6, vdim=10, kv_rank=20, q_rank=18, base=777.0)
+    return model([layer(mixer(**m), dense(ff=44, limit=0.9)),
+                  layer(mixer(**dict(m, kv_from=0)), moe(ff=20, experts=6, top=2, count=3, keep=2, scale=0.8)),
+                  layer(mixer(heads=1, dim=6, rot_dim=2, vdim=6, kv_rank=10, q_rank=6), None)], vocab=101, width=40)
+
+
 def random_weights(cfg_json, seed, bf16=False, gain=1.0):
     cfg = C.dugopel_from_json(cfg_json)
     rng = np.random.default_rng(seed)
@@ -198,7 +206,7 @@ def test_block_manager_reserve_grows_and_reuses():
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
 @pytest.mark.parametrize("case", ["attention", "partial_rotation", "dense", "moe_groups", "moe_top1", "borrowed_cache",
-                                  "softcap_saturates", "mixed"])
+                                  "softcap_saturates", "mixed", "odd_sizes"])
 def test_whole_prompt_matches_reference(case, prec):
     layers = {
         "attention": [layer(mixer(), None)],
@@ -209,7 +217,7 @@ def test_whole_prompt_matches_reference(case, prec):
         "borrowed_cache": [layer(mixer(), None), layer(mixer(kv_from=0), dense()), layer(mixer(kv_from=0), None)],
         "softcap_saturates": [layer(mixer(), dense())],
     }
-    j = mixed_model() if case == "mixed" else model(layers[case], cap=0.8 if case == "softcap_saturates" else 12.0,
+    j = mixed_model() if case == "mixed" else odd_model() if case == "odd_sizes" else model(layers[case], cap=0.8 if case == "softcap_saturates" else 12.0,
                                                      emb=1.0 if case == "dense" else 3.0)
     cfg, w = random_weights(j, 11, bf16=prec == C.PREC_BF16)
     toks = prompt(cfg, 45, 5)
@@ -235,8 +243,9 @@ def test_group_limit_and_raw_weights_change_the_result():
 # ------------------------------------------------------------------ GPU: cache, portions, batches
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
-def test_prefill_against_token_by_token_decoding(prec):
-    j = mixed_model()
+@pytest.mark.parametrize("make", [mixed_model, odd_model])
+def test_prefill_against_token_by_token_decoding(make, prec):
+    j = make()
     cfg, w = random_weights(j, 3, bf16=prec == C.PREC_BF16)
     toks = prompt(cfg, 40, 9)
     want = ref.forward(j, w, toks)
