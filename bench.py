@@ -490,6 +490,10 @@ DESIGN_SIZES = {
     "dense-1b": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 64, 512, 128),
     "dense-1b-long": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256, share=2),
                       "llama-3.2-1b", 16, 4096, 64),
+    # decode with enough cached rows per layer for bandwidth to matter (about 85 MB of latent rows,
+    # 545 MB of K / V)
+    "dense-1b-batch": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 128, 2048,
+                       32),
     "moe-1b": (lambda: dugopel_cfg(1024, 24, 16, 64, 32, 64, 96, 384, 512, 49155, moe=(32, 8, 8, 4)),
                "granite-moe-1b", 128, 128, 128),
 }
@@ -558,6 +562,11 @@ def design_bench(args):
                     else:
                         r["gbs"] = round(v["bytes"] / v["ms"] / 1e6, 1)
                         r["frac_of_measured_hbm"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+                    # the class's own roofline: the slower of its algorithmic bytes at the measured copy
+                    # bandwidth and its flops at the measured GEMM rate, over the time it took
+                    floor_ms = max(v["bytes"] / (peaks["hbm_gbs"] * 1e6), v["flops"] / (peaks["bf16_tflops_sustained"] * 1e9))
+                    r["roofline_us"] = round(floor_ms * 1e3 / n_steps, 2)
+                    r["frac_of_roofline"] = round(floor_ms / v["ms"], 3)
                     rows[k] = r
                 return rows
 

@@ -237,9 +237,9 @@ struct nvllm_handle {
   cudaGraphExec_t step_graph[2] = {nullptr, nullptr};
   struct GraphSig {
     const int32_t* d = nullptr;
-    int n = 0, max_blocks = 0, n_splits = 0;
+    int n = 0, n_out = 0, max_blocks = 0, n_splits = 0;
     bool operator==(const GraphSig& o) const {
-      return d == o.d && n == o.n && max_blocks == o.max_blocks && n_splits == o.n_splits;
+      return d == o.d && n == o.n && n_out == o.n_out && max_blocks == o.max_blocks && n_splits == o.n_splits;
     }
   } graph_sig[2];
   int graph_launches[2] = {0, 0};

@@ -98,6 +98,7 @@ static int graphed_step(nvllm_handle* h, int slot, Pre pre, bool* used) {
   nvllm_handle::GraphSig sig;
   sig.d = L.d;
   sig.n = L.n;
+  sig.n_out = L.n_out;  // requested logits rows change the staged layout and the head GEMM's rows
   sig.max_blocks = L.max_blocks;
   if (h->layered) {
     // every layer picks its own key split from (batch, its heads, longest context)

@@ -61,7 +61,10 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, ech
                 done[e["id"]] = len(seq)
             if seqs:
                 run.request_logits(rows)
-                run.run_flat([s.token_ids for s in seqs], True, num_cached=cached,
+                # a step of single continuing tokens is a decode step, as the engine issues it
+                # (key splits, replayed graph); anything else is a ragged prefill step
+                decode = all(len(s) - c == 1 and c > 0 for s, c in zip(seqs, cached))
+                run.run_flat([s.token_ids for s in seqs], not decode, num_cached=cached,
                              block_tables=[s.block_table for s in seqs], temperature=[0.0] * len(seqs))
                 if rows:
                     logits = run.fetch_logits(len(rows))

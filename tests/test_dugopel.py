@@ -479,6 +479,41 @@ def test_trace_replay_from_a_model_directory():
 
 
 @gpu
+@pytest.mark.parametrize("dtype,prec", [("float32", C.PREC_FP32), ("bfloat16", C.PREC_BF16)])
+def test_trace_replay_decoding_with_changing_requests(dtype, prec):
+    """Steps of single continuing tokens (issued as decode steps, replayed from a captured graph)
+    in which the set of live requests and the number of logits asked for change from step to step."""
+    from st_writer import write_safetensors
+    TR = nvllm_pkg.sub("trace")
+    j = mixed_model()
+    cfg, w = random_weights(j, 16, bf16=True)
+    toks = {"a": prompt(cfg, 40, 1), "b": prompt(cfg, BLOCK + 9, 2), "c": prompt(cfg, 23, 3)}
+    want = {k: ref.forward(j, w, t) for k, t in toks.items()}
+    tail = 14
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": t[:-tail], "want": []} for k, t in toks.items()], "end": []}]
+    asked = {}
+    for i in range(tail):
+        who = [k for k in toks if not (k == "c" and i in (3, 4)) and not (k == "a" and i >= 9)]
+        lag = {"a": 0, "b": 0, "c": 2 if i > 4 else 0}   # c sat out two steps: it is two tokens behind
+        entries = []
+        for n, k in enumerate(who):
+            at = len(toks[k]) - tail + i - lag[k]
+            w_ = [0] if n < i % (len(who) + 1) else []    # 0, 1, 2 or 3 rows of the step are asked for
+            entries.append({"id": k, "tokens": toks[k][at:at + 1], "want": w_})
+            if w_:
+                asked.setdefault(i + 1, []).append((k, at))
+        steps.append({"step": i + 1, "entries": entries, "end": ["a"] if i == 8 else []})
+    with tempfile.TemporaryDirectory() as d:
+        json.dump(j, open(os.path.join(d, "config.json"), "w"))
+        write_safetensors(os.path.join(d, "model.safetensors"), w, dtype="BF16")
+        TR.replay(d, dtype, os.path.join(d, "out"), 3 * BLOCK, [json.dumps(s) for s in steps], echo=lambda s: None)
+        assert len({len(v) for v in asked.values()}) >= 3
+        for n, rows in asked.items():
+            got = np.fromfile(os.path.join(d, "out", "%d.f32" % n), "<f4").reshape(-1, cfg.vocab_size)
+            check(got, np.stack([want[k][at] for k, at in rows]), prec, f"step {n}")
+
+
+@gpu
 def test_bad_configurations_are_refused():
     R = nvllm_pkg.sub("runner")
     L = nvllm_pkg.sub("lib")
