@@ -354,12 +354,16 @@ __global__ void __launch_bounds__(LAT_WARPS * 32) latent_attn_kernel(LatentArgs 
 // (ldmatrix.trans), so a cached row is staged once for both.  Online softmax in the accumulator
 // layout; the P fragments come straight from the score accumulators.
 constexpr int LM_KT = 64;
-template <int NR, int LM_ROWS>
-__global__ void __launch_bounds__(LM_ROWS * 2) latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
+// KS > 0: the cached row is exactly KS * 16 columns and R exactly NR * 8 (the common sizes): row
+// strides, loop counts and fragment addresses are then compile-time constants and the score loop
+// is unrolled; KS == 0 reads them from the arguments.
+template <int NR, int LM_ROWS, int KS>
+__global__ void __launch_bounds__(LM_ROWS * 2, (NR <= 16 && LM_ROWS == 128) ? 2 : 1)
+latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   extern __shared__ __align__(16) uint8_t smem_lm[];
-  const int Dk = a.R + a.rot, ld = Dk + 8, cpr = Dk / 8;
+  const int Dk = KS ? KS * 16 : a.R + a.rot, ld = Dk + 8, cpr = Dk / 8;
   const uint32_t sQ = smem_addr(smem_lm);
   const uint32_t sK0 = sQ + LM_ROWS * ld * 2;
   const uint32_t tile_bytes = LM_KT * ld * 2;
@@ -420,7 +424,7 @@ __global__ void __launch_bounds__(LM_ROWS * 2) latent_attn_mma_kernel(LatentArgs
     for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const float scale_log2 = a.scale * 1.4426950408889634f;
-  const int nks = Dk / 16, nrt = a.R / 8;
+  const int nks = KS ? KS : Dk / 16, nrt = KS ? NR : a.R / 8;
 
   int buf = 0;
   for (int kt = kt0; kt < kt1; kt++) {
@@ -439,7 +443,7 @@ __global__ void __launch_bounds__(LM_ROWS * 2) latent_attn_mma_kernel(LatentArgs
     for (int nt = 0; nt < 8; nt++)
 #pragma unroll
       for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
-    for (int ks = 0; ks < nks; ks++) {
+    auto score_step = [&](int ks) {
       uint32_t q0r, q1r, q2r, q3r;
       ldsm_x4(sQ + ((warp * 16 + lr + (mi & 1) * 8) * ld + (ks * 2 + (mi >> 1)) * 8) * 2, q0r, q1r, q2r, q3r);
 #pragma unroll
@@ -449,6 +453,12 @@ __global__ void __launch_bounds__(LM_ROWS * 2) latent_attn_mma_kernel(LatentArgs
         mma16816(s[nt], q0r, q1r, q2r, q3r, b0, b1);
         mma16816(s[nt + 1], q0r, q1r, q2r, q3r, b2, b3);
       }
+    };
+    if constexpr (KS > 0) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ks++) score_step(ks);
+    } else {
+      for (int ks = 0; ks < nks; ks++) score_step(ks);
     }
     // causal mask (keys past the CTA's range are zero-filled and masked the same way)
 #pragma unroll
@@ -553,17 +563,28 @@ static bool latent_mma_ok(int qdt, int kvdt, const LatentArgs& a) {
   return latent_mma_enabled() && qdt == DT_BF16 && kvdt == DT_BF16 && ((a.R + a.rot) % 16) == 0 && (a.R % 16) == 0 &&
          a.R <= 256 && a.scale > 0.f;
 }
-template <int NR, int ROWS>
-static cudaError_t launch_latent_mma_r(cudaStream_t st, const LatentArgs& a, int ns) {
+template <int NR, int ROWS, int KS>
+static cudaError_t launch_latent_mma_ks(cudaStream_t st, const LatentArgs& a, int ns) {
   const int Dk = a.R + a.rot;
   const size_t one = (size_t)LM_KT * (Dk + 8) * 2, qb = (size_t)ROWS * (Dk + 8) * 2;
   const int two = qb + 2 * one <= 200 * 1024 ? 1 : 0;
   const size_t smem = qb + one * (two ? 2 : 1);
   if (smem > 48 * 1024)
-    cudaFuncSetAttribute(latent_attn_mma_kernel<NR, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NR, ROWS, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, ROWS), ns);
-  (void)launch_k(latent_attn_mma_kernel<NR, ROWS>, grid, dim3(ROWS * 2), smem, st, a, two, next_trace(22));
+  (void)launch_k(latent_attn_mma_kernel<NR, ROWS, KS>, grid, dim3(ROWS * 2), smem, st, a, two, next_trace(22));
   return cudaGetLastError();
+}
+// rows of kv_rank = NR * 8 with a rotated part of 16, 32 or 64 take the kernel specialised on the row size
+template <int NR, int ROWS>
+static cudaError_t launch_latent_mma_r(cudaStream_t st, const LatentArgs& a, int ns) {
+  static const bool fixed = !(getenv("NVLLM_LATENT_FIXED") && atoi(getenv("NVLLM_LATENT_FIXED")) == 0);
+  if (fixed && a.R == NR * 8) {
+    if (a.rot == 16) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 1>(st, a, ns);
+    if (a.rot == 32) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 2>(st, a, ns);
+    if (a.rot == 64) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 4>(st, a, ns);
+  }
+  return launch_latent_mma_ks<NR, ROWS, 0>(st, a, ns);
 }
 // 128 items per CTA (8 warps) when a tile has that many: each staged key tile then serves twice the rows
 template <int NR>

@@ -339,10 +339,12 @@ def test_a_far_key_that_stands_out_is_found():
 
 
 @gpu
-@pytest.mark.parametrize("kv_rank,rot_dim,heads", [(32, 16, 3), (80, 16, 5), (144, 32, 2), (64, 16, 20)])
+@pytest.mark.parametrize("kv_rank,rot_dim,heads", [(32, 16, 3), (80, 16, 5), (144, 32, 2), (64, 16, 20),
+                                                  (64, 32, 3), (64, 64, 2), (128, 16, 9), (128, 32, 4), (256, 64, 2)])
 def test_tensor_core_attention_shapes(kv_rank, rot_dim, heads):
-    """bf16 cache rows whose sizes are multiples of 16 take the mma.sync attention kernel: whole
-    prompt, a ragged portion, and decoding with the keys split over several blocks of threads."""
+    """bf16 cache rows whose sizes are multiples of 16 take the mma.sync attention kernel (rows of
+    64 / 128 / 256 + 16 / 32 / 64 its variants with compile-time sizes; 9 and 20 heads fill CTAs of 128
+    rows): whole prompt, a ragged portion, and decoding with the keys split over several blocks of threads."""
     j = model([layer(mixer(heads=heads, kv_rank=kv_rank, rot_dim=rot_dim, scale=0.6), None),
                layer(mixer(heads=heads, kv_rank=kv_rank, rot_dim=rot_dim, kv_from=0), dense())])
     cfg, w = random_weights(j, 31, bf16=True)
