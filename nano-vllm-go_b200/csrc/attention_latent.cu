@@ -358,7 +358,7 @@ constexpr int LM_KT = 64;
 // strides, loop counts and fragment addresses are then compile-time constants and the score loop
 // is unrolled; KS == 0 reads them from the arguments.
 template <int NR, int LM_ROWS, int KS>
-__global__ void __launch_bounds__(LM_ROWS * 2, (NR <= 16 && LM_ROWS == 128) ? 2 : 1)
+__global__ void __launch_bounds__(LM_ROWS < 64 ? 128 : LM_ROWS * 2, (NR <= 16 && LM_ROWS == 128) ? 2 : 1)
 latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
@@ -368,6 +368,7 @@ latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
   const uint32_t sK0 = sQ + LM_ROWS * ld * 2;
   const uint32_t tile_bytes = LM_KT * ld * 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool active = LM_ROWS >= 64 || warp * 16 < LM_ROWS;  // warps beyond the CTA's rows only stage tiles
   const int g = lane >> 2, t = lane & 3, mi = lane >> 3, lr = lane & 7;
   pdl_wait();
   const int tile = blockIdx.x;
@@ -438,78 +439,80 @@ latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
     __syncthreads();
     const uint32_t sK = sK0 + (two_stage ? buf : 0) * tile_bytes;
     const int kpos0 = kt * LM_KT;
-    float s[8][4];
+    if (active) {
+      float s[8][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; nt++)
+      for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-      for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
-    auto score_step = [&](int ks) {
-      uint32_t q0r, q1r, q2r, q3r;
-      ldsm_x4(sQ + ((warp * 16 + lr + (mi & 1) * 8) * ld + (ks * 2 + (mi >> 1)) * 8) * 2, q0r, q1r, q2r, q3r);
+        for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
+      auto score_step = [&](int ks) {
+        uint32_t q0r, q1r, q2r, q3r;
+        ldsm_x4(sQ + ((warp * 16 + lr + (mi & 1) * 8) * ld + (ks * 2 + (mi >> 1)) * 8) * 2, q0r, q1r, q2r, q3r);
 #pragma unroll
-      for (int nt = 0; nt < 8; nt += 2) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4(sK + ((nt * 8 + lr + (mi >> 1) * 8) * ld + (ks * 2 + (mi & 1)) * 8) * 2, b0, b1, b2, b3);
-        mma16816(s[nt], q0r, q1r, q2r, q3r, b0, b1);
-        mma16816(s[nt + 1], q0r, q1r, q2r, q3r, b2, b3);
+        for (int nt = 0; nt < 8; nt += 2) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(sK + ((nt * 8 + lr + (mi >> 1) * 8) * ld + (ks * 2 + (mi & 1)) * 8) * 2, b0, b1, b2, b3);
+          mma16816(s[nt], q0r, q1r, q2r, q3r, b0, b1);
+          mma16816(s[nt + 1], q0r, q1r, q2r, q3r, b2, b3);
+        }
+      };
+      if constexpr (KS > 0) {
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) score_step(ks);
+      } else {
+        for (int ks = 0; ks < nks; ks++) score_step(ks);
       }
-    };
-    if constexpr (KS > 0) {
-#pragma unroll
-      for (int ks = 0; ks < KS; ks++) score_step(ks);
-    } else {
-      for (int ks = 0; ks < nks; ks++) score_step(ks);
-    }
-    // causal mask (keys past the CTA's range are zero-filled and masked the same way)
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-      const int kp = kpos0 + nt * 8 + 2 * t;
-      if (kp > limit[0]) s[nt][0] = -INFINITY;
-      if (kp + 1 > limit[0]) s[nt][1] = -INFINITY;
-      if (kp > limit[1]) s[nt][2] = -INFINITY;
-      if (kp + 1 > limit[1]) s[nt][3] = -INFINITY;
-    }
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-      float mx = -INFINITY;
-#pragma unroll
-      for (int nt = 0; nt < 8; nt++) mx = fmaxf(mx, fmaxf(s[nt][2 * i], s[nt][2 * i + 1]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m[i], mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f((m[i] - m_use) * scale_log2);  // m = -inf => 0
-      m[i] = m_new;
-      l[i] *= corr;
-#pragma unroll
-      for (int dn = 0; dn < NR; dn++) {
-        o[dn][2 * i] *= corr;
-        o[dn][2 * i + 1] *= corr;
-      }
-      float rs = 0.f;
+      // causal mask (keys past the CTA's range are zero-filled and masked the same way)
 #pragma unroll
       for (int nt = 0; nt < 8; nt++) {
-        const float p0 = exp2f((s[nt][2 * i] - m_use) * scale_log2);
-        const float p1 = exp2f((s[nt][2 * i + 1] - m_use) * scale_log2);
-        s[nt][2 * i] = p0;
-        s[nt][2 * i + 1] = p1;
-        rs += p0 + p1;
+        const int kp = kpos0 + nt * 8 + 2 * t;
+        if (kp > limit[0]) s[nt][0] = -INFINITY;
+        if (kp + 1 > limit[0]) s[nt][1] = -INFINITY;
+        if (kp > limit[1]) s[nt][2] = -INFINITY;
+        if (kp + 1 > limit[1]) s[nt][3] = -INFINITY;
       }
-      l[i] += rs;  // per-thread partial; the quad is reduced once at the end
-    }
 #pragma unroll
-    for (int kk = 0; kk < 4; kk++) {
-      const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      const uint32_t a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      for (int i = 0; i < 2; i++) {
+        float mx = -INFINITY;
 #pragma unroll
-      for (int dn = 0; dn < NR; dn += 2) {
-        if (dn < nrt) {
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4_t(sK + ((kk * 16 + lr + (mi & 1) * 8) * ld + (dn + (mi >> 1)) * 8) * 2, b0, b1, b2, b3);
-          mma16816(o[dn], a0, a1, a2, a3, b0, b1);
-          mma16816(o[dn + 1], a0, a1, a2, a3, b2, b3);
+        for (int nt = 0; nt < 8; nt++) mx = fmaxf(mx, fmaxf(s[nt][2 * i], s[nt][2 * i + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[i], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = exp2f((m[i] - m_use) * scale_log2);  // m = -inf => 0
+        m[i] = m_new;
+        l[i] *= corr;
+#pragma unroll
+        for (int dn = 0; dn < NR; dn++) {
+          o[dn][2 * i] *= corr;
+          o[dn][2 * i + 1] *= corr;
+        }
+        float rs = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+          const float p0 = exp2f((s[nt][2 * i] - m_use) * scale_log2);
+          const float p1 = exp2f((s[nt][2 * i + 1] - m_use) * scale_log2);
+          s[nt][2 * i] = p0;
+          s[nt][2 * i + 1] = p1;
+          rs += p0 + p1;
+        }
+        l[i] += rs;  // per-thread partial; the quad is reduced once at the end
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) {
+        const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        const uint32_t a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dn = 0; dn < NR; dn += 2) {
+          if (dn < nrt) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(sK + ((kk * 16 + lr + (mi & 1) * 8) * ld + (dn + (mi >> 1)) * 8) * 2, b0, b1, b2, b3);
+            mma16816(o[dn], a0, a1, a2, a3, b0, b1);
+            mma16816(o[dn + 1], a0, a1, a2, a3, b2, b3);
+          }
         }
       }
     }
@@ -527,7 +530,7 @@ latent_attn_mma_kernel(LatentArgs a, int two_stage, Trace tr) {
 #pragma unroll
   for (int i = 0; i < 2; i++) {
     const int item = item0 + warp * 16 + g + 8 * i;
-    if (item >= n_items) continue;
+    if (!active || item >= n_items) continue;
     const size_t it = (size_t)(row0 + q0) * a.H + item;  // row * H + head
     if (gridDim.z == 1) {
       const int row = row0 + q0 + item / a.H, head = item % a.H;
@@ -572,14 +575,18 @@ static cudaError_t launch_latent_mma_ks(cudaStream_t st, const LatentArgs& a, in
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(latent_attn_mma_kernel<NR, ROWS, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(a.n_tiles, ceil_div(a.qtile * a.H, ROWS), ns);
-  (void)launch_k(latent_attn_mma_kernel<NR, ROWS, KS>, grid, dim3(ROWS * 2), smem, st, a, two, next_trace(22));
+  // CTAs of fewer than 64 rows: a few of them per SM are bound by the latency of staging a key
+  // tile, so two more warps help with the copies; many per SM are bound by the tensor pipe, and
+  // idle warps would only take registers from resident CTAs
+  int threads = ROWS * 2;
+  if (ROWS < 64 && (long)grid.x * grid.y * grid.z < 3L * a.sm_count) threads = 128;
+  (void)launch_k(latent_attn_mma_kernel<NR, ROWS, KS>, grid, dim3(threads), smem, st, a, two, next_trace(22));
   return cudaGetLastError();
 }
 // rows of kv_rank = NR * 8 with a rotated part of 16, 32 or 64 take the kernel specialised on the row size
 template <int NR, int ROWS>
 static cudaError_t launch_latent_mma_r(cudaStream_t st, const LatentArgs& a, int ns) {
-  static const bool fixed = !(getenv("NVLLM_LATENT_FIXED") && atoi(getenv("NVLLM_LATENT_FIXED")) == 0);
-  if (fixed && a.R == NR * 8) {
+  if (a.R == NR * 8) {
     if (a.rot == 16) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 1>(st, a, ns);
     if (a.rot == 32) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 2>(st, a, ns);
     if (a.rot == 64) return launch_latent_mma_ks<NR, ROWS, NR / 2 + 4>(st, a, ns);
@@ -589,7 +596,10 @@ static cudaError_t launch_latent_mma_r(cudaStream_t st, const LatentArgs& a, int
 // 128 items per CTA (8 warps) when a tile has that many: each staged key tile then serves twice the rows
 template <int NR>
 static cudaError_t launch_latent_mma(cudaStream_t st, const LatentArgs& a, int ns) {
-  if (NR <= 16 && a.qtile * a.H >= 128) return launch_latent_mma_r<NR, 128>(st, a, ns);
+  const int items = a.qtile * a.H;
+  if (NR <= 16 && items >= 128) return launch_latent_mma_r<NR, 128>(st, a, ns);
+  if (items <= 16) return launch_latent_mma_r<NR, 16>(st, a, ns);
+  if (items <= 32) return launch_latent_mma_r<NR, 32>(st, a, ns);
   return launch_latent_mma_r<NR, 64>(st, a, ns);
 }
 

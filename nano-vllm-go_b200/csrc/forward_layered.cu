@@ -261,6 +261,7 @@ int forward_step_layered(nvllm_handle* h) {
     a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
     a.olat = w.lat_o;
     a.split_ws = w.attn_ws;
+    a.sm_count = h->sm_count;
     if (L.prefill) {
       a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles;
       a.qtile = LAT_QTILE; a.n_splits = 1;

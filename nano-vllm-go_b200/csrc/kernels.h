@@ -370,6 +370,7 @@ struct LatentArgs {
   void* qabs;
   // attention
   const int* block_tables; int max_blocks;
+  int sm_count;
   const int *cu_q, *seq_start, *seq_len, *tile_seq, *tile_q0;  // without a tile list: one new token per sequence at seq_len - 1
   int n_tiles, qtile, n_splits;
   float* split_ws;                   // [T, H, n_splits, R + 2]
