@@ -237,7 +237,14 @@ def test_group_limit_and_raw_weights_change_the_result():
     want = ref.forward(j, w, toks)
     j2 = copy.deepcopy(j)
     j2["layers"][0]["mlp"]["router"]["groups"] = {"count": 1, "keep": 1}
-    assert np.abs(ref.forward(j2, w, toks) - want).max() > 1e-2
+    free = ref.forward(j2, w, toks)
+    assert np.abs(free - want).max() > 1e-2
+    for jj, target, other in ((j, want, free), (j2, free, want)):
+        eng = Engine(C.dugopel_from_json(jj), w, C.PREC_FP32)
+        got, _ = eng.step([("a", toks, list(range(len(toks))))])
+        eng.close()
+        check(got, target, C.PREC_FP32, "routing")
+        assert np.abs(got - other).max() > 1e-2
 
 
 # ------------------------------------------------------------------ GPU: cache, portions, batches
