@@ -436,6 +436,72 @@ def test_long_decoding_through_the_resident_loop():
     assert np.array_equal(pred[sure[len(toks) - 1:]], np.array(gen)[sure[len(toks) - 1:]])
 
 
+def random_model(seed):
+    """A model drawn at random: sizes, head counts, layer order, feed-forward kinds, borrowed caches."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *a: a[int(rng.integers(len(a)))]
+    caches = [dict(kv_rank=pick(8, 20, 32, 48, 64, 72, 128), rot_dim=pick(2, 6, 8, 16, 32),
+                   base=pick(100.0, 10000.0, 500000.0)) for _ in range(2)]
+    layers, owners = [], {}
+    for l in range(int(rng.integers(2, 7))):
+        ci = int(rng.integers(2))
+        m = dict(caches[ci], heads=pick(1, 2, 3, 4, 6, 7), dim=pick(4, 8, 12, 16, 24, 32), vdim=pick(4, 8, 20, 32, 48),
+                 q_rank=pick(8, 12, 24, 40, 64))
+        if ci in owners and rng.random() < 0.6:
+            m["kv_from"] = owners[ci]
+        else:
+            owners.setdefault(ci, l)
+        kind = pick("none", "dense", "moe", "moe")
+        if kind == "moe":
+            count = pick(1, 2, 3, 4)
+            per = pick(1, 2, 3)
+            keep = int(rng.integers(1, count + 1))
+            mlp = moe(ff=pick(8, 12, 24, 40), limit=pick(0.5, 1.0, 3.0, 7.0), experts=count * per,
+                      top=int(rng.integers(1, keep * per + 1)), count=count, keep=keep, scale=pick(0.5, 1.0, 2.5))
+        else:
+            mlp = dense(ff=pick(8, 20, 48, 96), limit=pick(0.5, 1.0, 7.0)) if kind == "dense" else None
+        layers.append(layer(mixer(**m), mlp))
+    return model(layers, vocab=pick(37, 128, 333, 1000), width=pick(24, 40, 64, 96, 136), eps=pick(1e-5, 1e-6),
+                 emb=pick(1.0, 4.0, 12.0), cap=pick(5.0, 30.0))
+
+
+@gpu
+@pytest.mark.parametrize("prec", PRECS)
+@pytest.mark.parametrize("seed", range(8))
+def test_models_drawn_at_random(seed, prec):
+    """Whole prompt, the same prompt in portions with its tail decoded one by one, and a second
+    request beside it: every logit against the reference."""
+    j = random_model(100 + seed)
+    cfg, w = random_weights(j, 200 + seed, bf16=prec == C.PREC_BF16)
+    a, b = prompt(cfg, BLOCK + 31, seed), prompt(cfg, 19, 50 + seed)
+    wa, wb = ref.forward(j, w, a), ref.forward(j, w, b)
+    eng = Engine(cfg, w, prec, num_blocks=5)
+    got, _ = eng.step([("w", a, list(range(len(a))))])
+    check(got, wa, prec, f"whole prompt of {json.dumps(j)}")
+    eng.end("w")
+    rows, at = [], 0
+    for n in (5, 2, BLOCK - 10, 9, 17):
+        entries = [("a", a[at:at + n], list(range(n)))]
+        if at == 7:
+            entries.append(("b", b[:-2], [0, len(b) - 3]))
+        g = eng.step(entries)[0]
+        rows.append(g[:n])
+        if len(entries) == 2:
+            check(g[n:], wb[[0, len(b) - 3]], prec, "second request's prompt")
+        at += n
+    while at < len(a):
+        entries = [("a", a[at:at + 1], [0])]
+        if at >= len(a) - 2:
+            entries.append(("b", b[at - len(a):][:1], [0]))
+        g = eng.step(entries, decode=at != len(a) - 5)[0]   # one single token goes through the ragged path
+        rows.append(g[:1])
+        if len(entries) == 2:
+            check(g[1:], wb[[len(b) + at - len(a)]], prec, "second request")
+        at += 1
+    eng.close()
+    check(np.concatenate(rows), wa, prec, "portions and decoding")
+
+
 # ------------------------------------------------------------------ GPU: through the engine and from a directory
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
