@@ -130,7 +130,11 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     w.max_tiles = (int)(P / 32 + h->E);  // token tiles are >= 32 rows
     WS(w.xn_f32, Tc * H * 4);
     WS(w.topk_idx, P * 4);
-    WS(w.topk_w, P * 4);
+    // A routed layer's norm kernel combines the previous routed layer's experts (reading that
+    // layer's weights, k_prev per row) while it writes its own (k per row): with k != k_prev the
+    // rows of different CTAs would overlap in one buffer, so consecutive routed layers alternate.
+    w.topk_pairs = P;
+    WS(w.topk_w, 2 * P * 4);
     WS(w.sort.counts, h->E * 4);
     WS(w.sort.offsets, (h->E + 1) * 4);
     WS(w.sort.cursor, h->E * 4);
@@ -437,7 +441,7 @@ int forward_step(nvllm_handle* h) {
     }
     Pending& pf = h->parallel ? p2 : p1;
     if (h->moe) {
-      if ((rc = run_moe_ffn(h, T, w.xn, h->E, h->topk, h->F, 0.f, lw.moe_in, lw.moe_out, &pf))) return rc;
+      if ((rc = run_moe_ffn(h, T, w.xn, h->E, h->topk, h->F, 0.f, lw.moe_in, lw.moe_out, w.topk_w, &pf))) return rc;
     } else {
       // decode-sized steps: W1 (+ fused activation) and W2 in ONE launch — W2's weight stream
       // starts under W1's epilogues and the launch / drain / release gap between the two

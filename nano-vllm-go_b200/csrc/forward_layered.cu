@@ -229,13 +229,16 @@ int forward_step_layered(nvllm_handle* h) {
     LAUNCH(h, launch_rope_table(st, d_pos, T, r.dims / 2, r.inv_freq, r.cosT, r.sinT));
   }
   Pending p1, p2;
+  int routed = 0;  // routed layers so far: picks the half of topk_w this layer writes
   for (int l = 0; l < h->L; l++) {
     const ListedLayer& y = h->ll[l];
     const nvllm_layer_spec& s = y.s;
     RouterArgs ra;
+    float* topk_w = w.topk_w;
     if (s.mlp == NVLLM_MLP_MOE) {
+      topk_w += (size_t)(routed++ & 1) * w.topk_pairs;
       ra.R = y.router; ra.E = s.experts; ra.k = s.top;
-      ra.topk_idx = w.topk_idx; ra.topk_w = w.topk_w;
+      ra.topk_idx = w.topk_idx; ra.topk_w = topk_w;
       ra.opts = RouteOpts{s.groups, s.keep_groups, 1, s.router_scale};
     }
     if ((rc = run_norm(h, w.x, &p1, &p2, y.norm_w, nullptr, w.xn, nullptr, nullptr, T,
@@ -323,7 +326,7 @@ int forward_step_layered(nvllm_handle* h) {
         if ((rc = run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_c, w.ws_b_floats, H, &pm))) return rc;
       }
     } else if (s.mlp == NVLLM_MLP_MOE) {
-      if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, y.ff_p, s.limit, y.moe_in, y.moe_out, &pm))) return rc;
+      if ((rc = run_moe_ffn(h, T, w.xn, s.experts, s.top, y.ff_p, s.limit, y.moe_in, y.moe_out, topk_w, &pm))) return rc;
     }
     if (pm.p) {
       p1 = pm;  // the expert combine can only be the first addend of the norm kernel

@@ -252,9 +252,11 @@ static int run_norm(nvllm_handle* h, float* x, Pending* p1, Pending* p2, const f
 // Mixture-of-experts feed-forward of T routed tokens (the routing itself ran inside the norm
 // kernel that produced xn): group the (token, slot) pairs by expert, two grouped GEMMs with the
 // gated unit between them.  E experts of inner size I, k per token; glu_limit > 0 selects the
-// clamped gated unit.  Leaves the expert outputs pending in *pf (combined by the next norm).
+// clamped gated unit; topk_w holds this layer's routing weights.  Leaves the expert outputs
+// pending in *pf (combined by the next norm).
 static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int I, float glu_limit,
-                       const void* moe_in, const void* moe_out, Pending* pf) {
+                       const void* moe_in, const void* moe_out, const float* topk_w,
+                       Pending* pf) {
   const int H = h->H;
   const int P = T * k;
   Workspace& w = h->ws;
@@ -334,7 +336,7 @@ static int run_moe_ffn(nvllm_handle* h, int T, const void* xn, int E, int k, int
   }
   // the weighted combine (moe.go:116-118) happens inside the norm kernel that consumes pf
   pf->p = w.moe_Y; pf->S = 1; pf->stride = 0; pf->bias = nullptr;
-  pf->comb_rows = w.sort.pair_row; pf->comb_w = w.topk_w; pf->comb_k = k;
+  pf->comb_rows = w.sort.pair_row; pf->comb_w = topk_w; pf->comb_k = k;
   return NVLLM_OK;
 }
 

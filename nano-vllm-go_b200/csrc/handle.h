@@ -112,7 +112,8 @@ struct Workspace {
   int* amax_ticket = nullptr;          // [n]
   // moe
   int* topk_idx = nullptr;
-  float* topk_w = nullptr;
+  float* topk_w = nullptr;  // two halves of topk_pairs floats, used in turn by the routed layers
+  size_t topk_pairs = 0;
   MoeSortBufs sort{};
   int max_tiles = 0;
   // latent attention (forward_layered.cu)

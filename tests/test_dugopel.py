@@ -436,6 +436,26 @@ def test_long_decoding_through_the_resident_loop():
     assert np.array_equal(pred[sure[len(toks) - 1:]], np.array(gen)[sure[len(toks) - 1:]])
 
 
+@gpu
+@pytest.mark.parametrize("tops", [(1, 3, 2), (3, 1, 4), (2, 2, 1)])
+def test_routed_layers_with_unequal_top_counts_in_a_row(tops):
+    """Consecutive routed layers that keep different numbers of experts per token, on a prompt of
+    several waves of rows: the weights of one layer's experts are still being combined while the
+    next layer routes, and the two must not share storage row for row."""
+    m = dict(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=16)
+    layers = [layer(mixer(**m), moe(ff=16, limit=2.0, experts=6, top=tops[0], count=1, keep=1, scale=1.0)),
+              layer(mixer(**dict(m, kv_from=0)), moe(ff=8, limit=1.0, experts=4, top=tops[1], count=2, keep=2, scale=2.5)),
+              layer(mixer(**dict(m, kv_from=0)), None),
+              layer(mixer(**dict(m, kv_from=0)), moe(ff=24, limit=3.0, experts=8, top=tops[2], count=4, keep=2, scale=0.5))]
+    j = model(layers, vocab=97, width=48)
+    cfg, w = random_weights(j, 31)
+    toks = prompt(cfg, 2 * BLOCK + 90, 4)
+    eng = Engine(cfg, w, C.PREC_FP32, num_blocks=4)
+    got, _ = eng.step([("a", toks, list(range(len(toks))))])
+    eng.close()
+    check(got, ref.forward(j, w, toks), C.PREC_FP32, f"top counts {tops}")
+
+
 def random_model(seed):
     """A model drawn at random: sizes, head counts, layer order, feed-forward kinds, borrowed caches."""
     rng = np.random.default_rng(seed)
@@ -467,7 +487,7 @@ def random_model(seed):
 
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
-@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("NVLLM_TEST_RANDOM_MODELS", "8"))))
 def test_models_drawn_at_random(seed, prec):
     """Whole prompt, the same prompt in portions with its tail decoded one by one, and a second
     request beside it: every logit against the reference."""
