@@ -131,10 +131,11 @@ def tol(prec):
     return 2e-4 if prec == C.PREC_FP32 else 3e-2
 
 
-def check(got, want, prec, what=""):
+def check(got, want, prec, what="", ties=None):
     """fp32: every row within 2e-4 of the largest logit.  bf16: rounding of the residual stream
     can flip a close expert choice at a single position (no fault: the design's router is fp32 on a
-    bf16-rounded input), so up to one row in sixteen may be off by more — but never grossly."""
+    bf16-rounded input), so up to one row in sixteen may be off by more — but never grossly, except
+    at the rows `ties` marks (the reference's own choice there hangs on less than 1% probability)."""
     want = np.asarray(want).reshape(-1, np.asarray(want).shape[-1])
     got = np.asarray(got).reshape(want.shape)
     err = np.abs(got - want).max(-1) / np.abs(want).max()
@@ -142,6 +143,8 @@ def check(got, want, prec, what=""):
         assert err.max() <= tol(prec), f"{what}: relative error {err.max():.3g} at row {err.argmax()}"
         return
     over = int((err > tol(prec)).sum())
+    if ties is not None:
+        err = np.where(np.asarray(ties) & (err > 0.25), 0.25, err)
     assert over <= len(err) // 16 and err.max() <= 0.25 and np.median(err) <= tol(prec) / 3, \
         f"{what}: {over} of {len(err)} rows over {tol(prec)}, worst {err.max():.3g} at row {err.argmax()}, median {np.median(err):.3g}"
 
@@ -456,6 +459,32 @@ def test_routed_layers_with_unequal_top_counts_in_a_row(tops):
     check(got, ref.forward(j, w, toks), C.PREC_FP32, f"top counts {tops}")
 
 
+def routing_margins(j, w, toks):
+    """Per position, over the routed layers of the reference: how much probability separates the
+    routing that was chosen from the next one (the weakest kept group from the best dropped group,
+    the weakest chosen expert from the best candidate left out)."""
+    _, per = ref.forward(j, w, toks, keep_layers=True)
+    x = np.asarray(w["embed"], np.float64)[np.asarray(toks)] * j["embedding"]["scale"]
+    margin = np.full(len(toks), np.inf)
+    for i, lc in enumerate(j["layers"]):
+        if lc["mlp"] is not None and lc["mlp"]["kind"] == "moe":
+            rc = lc["mlp"]["router"]
+            G, keep, top = rc["groups"]["count"], rc["groups"]["keep"], rc["top"]
+            h = ref.layer_norm_noshift(x, w[f"l{i}.norm1"], j["norm"]["eps"])
+            s = ref.softmax(h @ np.asarray(w[f"l{i}.mlp.router"], np.float64).T)
+            gs = -np.sort(-s.reshape(len(toks), G, -1).max(-1), axis=-1)
+            if keep < G:
+                margin = np.minimum(margin, gs[:, keep - 1] - gs[:, keep])
+            idx, _ = ref.route(h, w[f"l{i}.mlp.router"], rc)
+            for t in range(len(toks)):
+                kept = np.argsort(-s[t].reshape(G, -1).max(-1), kind="stable")[:keep]
+                cand = [e for e in range(rc["experts"]) if e // (rc["experts"] // G) in kept and e not in idx[t]]
+                if cand:
+                    margin[t] = min(margin[t], s[t, idx[t]].min() - s[t, cand].max())
+        x = per[i]
+    return margin
+
+
 def random_model(seed):
     """A model drawn at random: sizes, head counts, layer order, feed-forward kinds, borrowed caches."""
     rng = np.random.default_rng(seed)
@@ -495,9 +524,10 @@ def test_models_drawn_at_random(seed, prec):
     cfg, w = random_weights(j, 200 + seed, bf16=prec == C.PREC_BF16)
     a, b = prompt(cfg, BLOCK + 31, seed), prompt(cfg, 19, 50 + seed)
     wa, wb = ref.forward(j, w, a), ref.forward(j, w, b)
+    ties = routing_margins(j, w, a) < 0.01 if prec == C.PREC_BF16 else None
     eng = Engine(cfg, w, prec, num_blocks=5)
     got, _ = eng.step([("w", a, list(range(len(a))))])
-    check(got, wa, prec, f"whole prompt of {json.dumps(j)}")
+    check(got, wa, prec, f"whole prompt of {json.dumps(j)}", ties)
     eng.end("w")
     rows, at = [], 0
     for n in (5, 2, BLOCK - 10, 9, 17):
@@ -519,7 +549,7 @@ def test_models_drawn_at_random(seed, prec):
             check(g[1:], wb[[len(b) + at - len(a)]], prec, "second request")
         at += 1
     eng.close()
-    check(np.concatenate(rows), wa, prec, "portions and decoding")
+    check(np.concatenate(rows), wa, prec, "portions and decoding", ties)
 
 
 # ------------------------------------------------------------------ GPU: through the engine and from a directory
