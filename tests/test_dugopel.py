@@ -134,8 +134,8 @@ def tol(prec):
 def check(got, want, prec, what="", ties=None):
     """fp32: every row within 2e-4 of the largest logit.  bf16: rounding of the residual stream
     can flip a close expert choice at a single position (no fault: the design's router is fp32 on a
-    bf16-rounded input), so up to one row in sixteen may be off by more — but never grossly, except
-    at the rows `ties` marks (the reference's own choice there hangs on less than 1% probability)."""
+    bf16-rounded input), so up to one row in sixteen may be off by more — but never grossly (and the median of a check of 8 rows or more stays at a
+    third of the tolerance), except at the rows `ties` marks (the reference's own choice there hangs on less than 1% probability)."""
     want = np.asarray(want).reshape(-1, np.asarray(want).shape[-1])
     got = np.asarray(got).reshape(want.shape)
     err = np.abs(got - want).max(-1) / np.abs(want).max()
@@ -145,7 +145,7 @@ def check(got, want, prec, what="", ties=None):
     over = int((err > tol(prec)).sum())
     if ties is not None:
         err = np.where(np.asarray(ties) & (err > 0.25), 0.25, err)
-    assert over <= len(err) // 16 and err.max() <= 0.25 and np.median(err) <= tol(prec) / 3, \
+    assert over <= len(err) // 16 and err.max() <= 0.25 and (len(err) < 8 or np.median(err) <= tol(prec) / 3), \
         f"{what}: {over} of {len(err)} rows over {tol(prec)}, worst {err.max():.3g} at row {err.argmax()}, median {np.median(err):.3g}"
 
 
