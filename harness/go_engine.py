@@ -51,6 +51,7 @@ class EngineConfig:  # config.go:9-70
     eos: int = -1
     kvcache_block_size: int = 256
     num_kvcache_blocks: int = -1
+    num_state_slots: int = 0  # > 0: the model keeps recurrent state per sequence (one slot each)
 
     def __post_init__(self):
         if self.kvcache_block_size % 256 != 0:
@@ -82,6 +83,8 @@ class Sequence:  # sequence.go:15-114
         self.max_tokens = sp.max_tokens
         self.ignore_eos = sp.ignore_eos
         self.block_size = 256  # sequence.go:52
+        # models with recurrent mixers: the slot that holds this sequence's state (BlockManager)
+        self.state_slot = -1
 
     def __len__(self):
         return self.num_tokens
@@ -133,12 +136,28 @@ class Block:  # block_manager.go:10-39
 
 
 class BlockManager:  # block_manager.go:41-263
-    def __init__(self, num_blocks: int, block_size: int):
+    def __init__(self, num_blocks: int, block_size: int, num_state_slots: int = 0):
+        """num_state_slots > 0: the model keeps recurrent state per sequence.  A sequence then
+        holds one state slot from its first block to deallocate(), and no cached prefix is ever
+        offered (blocks hold keys and values, not the state that goes with them)."""
         self.block_size = block_size
         self.blocks = [Block(i) for i in range(num_blocks)]
         self.hash_to_block_id: Dict[int, int] = {}
         self.free_block_ids: List[int] = list(range(num_blocks))
         self.used_block_ids: set = set()
+        self.num_state_slots = num_state_slots
+        self.free_state_slots: List[int] = list(range(num_state_slots))
+
+    def _take_state_slot(self, seq: Sequence):
+        if self.num_state_slots and seq.state_slot < 0:
+            if not self.free_state_slots:
+                raise RuntimeError("out of state slots")
+            seq.state_slot = self.free_state_slots.pop(0)
+
+    def _give_state_slot(self, seq: Sequence):
+        if seq.state_slot >= 0:
+            self.free_state_slots.append(seq.state_slot)
+            seq.state_slot = -1
 
     @staticmethod
     def compute_hash(token_ids: Seq[int], prefix_hash: int = 0) -> int:
@@ -165,13 +184,16 @@ class BlockManager:  # block_manager.go:41-263
         self.free_block_ids.append(block_id)
 
     def can_allocate(self, seq: Sequence) -> bool:
+        if self.num_state_slots and seq.state_slot < 0 and not self.free_state_slots:
+            return False
         return len(self.free_block_ids) >= seq.num_blocks()
 
     def allocate(self, seq: Sequence):  # block_manager.go:128-203
         if seq.block_table:
             raise RuntimeError("sequence already has blocks allocated")
+        self._take_state_slot(seq)
         h = 0
-        cache_miss = False
+        cache_miss = bool(self.num_state_slots)  # recurrent state: every prompt is computed in full
         for i in range(seq.num_blocks()):
             token_ids = seq.block(i)
             h = self.compute_hash(token_ids, h) if len(token_ids) == self.block_size else 0
@@ -189,7 +211,7 @@ class BlockManager:  # block_manager.go:41-263
                     self.blocks[block_id].ref_count += 1
                 else:
                     self._allocate_block(block_id)
-            if h != 0:
+            if h != 0 and not self.num_state_slots:
                 self.blocks[block_id].update(h, token_ids)
                 self.hash_to_block_id[h] = block_id
             seq.block_table.append(block_id)
@@ -201,6 +223,7 @@ class BlockManager:  # block_manager.go:41-263
         need = (num_tokens + self.block_size - 1) // self.block_size - len(seq.block_table)
         if need > len(self.free_block_ids):
             raise RuntimeError("out of cache blocks")
+        self._take_state_slot(seq)
         for _ in range(max(0, need)):
             block_id = self.free_block_ids[0]
             self._allocate_block(block_id)
@@ -214,6 +237,7 @@ class BlockManager:  # block_manager.go:41-263
                 self._deallocate_block(block_id)
         seq.num_cached_tokens = 0
         seq.block_table = []
+        self._give_state_slot(seq)
 
     def can_append(self, seq: Sequence) -> bool:  # :222-228
         if len(seq) % self.block_size == 1:
@@ -223,6 +247,12 @@ class BlockManager:  # block_manager.go:41-263
     def may_append(self, seq: Sequence):  # :231-263
         last_block = self.blocks[seq.block_table[-1]]
         m = len(seq) % self.block_size
+        if self.num_state_slots:  # no prefix hashes are kept for models with recurrent state
+            if m == 1:
+                block_id = self.free_block_ids[0]
+                self._allocate_block(block_id)
+                seq.block_table.append(block_id)
+            return
         if m == 1:
             if last_block.hash == 0:
                 raise RuntimeError("last block should have a hash")
@@ -248,7 +278,7 @@ class Scheduler:  # scheduler.go:6-140
         self.max_num_seqs = cfg.max_num_seqs
         self.max_num_batched_tokens = cfg.max_num_batched_tokens
         self.eos = cfg.eos
-        self.block_manager = BlockManager(num_blocks, cfg.kvcache_block_size)
+        self.block_manager = BlockManager(num_blocks, cfg.kvcache_block_size, cfg.num_state_slots)
         self.waiting: Deque[Sequence] = deque()
         self.running: Deque[Sequence] = deque()
 
@@ -332,6 +362,8 @@ class MockModelRunner:  # model_runner.go:19-55
 
 class LLMEngine:  # llm_engine.go:25-203 without the tokenizer / progress bar
     def __init__(self, cfg: EngineConfig, model_runner):
+        if getattr(model_runner, "needs_state_slots", False) and cfg.num_state_slots <= 0:
+            cfg.num_state_slots = cfg.max_num_seqs  # as many as the runner's default
         self.cfg = cfg
         self.model_runner = model_runner
         self.scheduler = Scheduler(cfg)

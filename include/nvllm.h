@@ -182,20 +182,36 @@ int nvllm_create(const nvllm_config* cfg, const uint8_t* tp_id, nvllm_handle** o
 /* ---- models given as a list of layers ------------------------------------
  * A model whose config.json lists its layers one by one (each with its own mixer and
  * feed-forward sizes) is created from an array of nvllm_layer_spec instead of the uniform
- * fields of nvllm_config.  Every layer is a parallel block: h = LayerNorm(x) (weight, no
- * additive term), x += mixer(h) + feed_forward(h).  Tensors are handed in by checkpoint name
- * (nvllm_set_named_weight, or nvllm_load_safetensors with NVLLM_ARCH_DUGOPEL). */
-enum nvllm_mixer_kind { NVLLM_MIXER_LATENT_ATTENTION = 1 };
+ * fields of nvllm_config.  nvllm_layered_config::block_style says how a layer combines its
+ * sublayers:
+ *   NVLLM_LBLOCK_PARALLEL_PRENORM   h = LayerNorm(x) (weight, no additive term),
+ *                                   x += mixer(h) + feed_forward(h)                   (Dugopel)
+ *   NVLLM_LBLOCK_SEQUENTIAL_POSTNORM  x += RMSNorm(mixer(x)), then x += RMSNorm(feed_forward(x)):
+ *                                   the sublayers read x itself, the norm sits on their output (Zozonex)
+ * Tensors are handed in by checkpoint name (nvllm_set_named_weight, or nvllm_load_safetensors
+ * with NVLLM_ARCH_DUGOPEL / NVLLM_ARCH_ZOZONEX). */
+enum nvllm_mixer_kind {
+  NVLLM_MIXER_LATENT_ATTENTION = 1,
+  NVLLM_MIXER_WINDOW_ATTENTION = 2, /* grouped-query attention over a sliding window of the paged K / V cache */
+  NVLLM_MIXER_DELTA = 3             /* gated delta rule: a recurrent dim x vdim state per head, kept per state slot */
+};
 enum nvllm_mlp_kind { NVLLM_MLP_NONE = 0, NVLLM_MLP_DENSE = 1, NVLLM_MLP_MOE = 2 };
+enum nvllm_ffn_act {
+  NVLLM_FFN_GLU_CLAMPED = 0, /* W_down (g sigmoid(1.702 g) (u + 1)), g / u clamped by `limit` */
+  NVLLM_FFN_RELU2 = 1        /* W_down relu(W_up h)^2 */
+};
+enum nvllm_layered_block { NVLLM_LBLOCK_PARALLEL_PRENORM = 0, NVLLM_LBLOCK_SEQUENTIAL_POSTNORM = 1 };
+enum nvllm_layered_position { NVLLM_LPOS_NONE = 0, NVLLM_LPOS_SINUSOIDAL = 1 };
 
 typedef struct nvllm_layer_spec {
   int32_t mixer;        /* nvllm_mixer_kind */
   /* latent attention: queries through a q_rank latent; keys / values through a kv_rank latent
    * plus one rotated key part of rot_dim shared by the heads.  Per head: dim unrotated and
-   * rot_dim rotated query / key entries, vdim value entries. */
+   * rot_dim rotated query / key entries, vdim value entries.
+   * window attention / delta rule: heads, dim (query / key entries per head), vdim. */
   int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank;
   int32_t rot_dims;     /* leading entries of the rotated part that are rotated (<= rot_dim, even) */
-  int32_t kv_from;      /* -1: own key/value down projection and cache; j: reads layer j's cache */
+  int32_t kv_from;      /* -1: own key/value projection and cache; j: reads layer j's cache */
   float rot_base;
   float scale;          /* multiplies the scores */
   int32_t mlp;          /* nvllm_mlp_kind */
@@ -204,6 +220,13 @@ typedef struct nvllm_layer_spec {
   int32_t experts, top; /* MoE: experts, experts per token */
   int32_t groups, keep_groups; /* MoE: equal groups of neighbouring experts, groups a token may use */
   float router_scale;   /* MoE: weights = softmax scores of the chosen experts * router_scale */
+  /* window attention / delta rule */
+  int32_t kv_heads;     /* key (delta rule: query and key) heads; head h uses head h / (heads / kv_heads) */
+  int32_t window;       /* window attention: position i sees j with 0 <= i - j < window; 0 = every j <= i */
+  int32_t sink;         /* window attention: 1 = the softmax denominator has one more term exp(0) without a value */
+  int32_t qk_norm;      /* window attention: 1 = q and k divided by their root mean square per head (eps of the model) */
+  int32_t conv;         /* delta rule: taps of the causal convolution over time on q, k, v */
+  int32_t act;          /* dense feed-forward: nvllm_ffn_act */
 } nvllm_layer_spec;
 
 typedef struct nvllm_layered_config {
@@ -214,6 +237,11 @@ typedef struct nvllm_layered_config {
   float logit_softcap;     /* logits <- cap * tanh(logits / cap); 0 = none */
   int32_t precision;       /* nvllm_precision */
   int32_t num_kv_blocks, max_num_seqs, max_batched_tokens, device;
+  int32_t block_style;     /* nvllm_layered_block */
+  int32_t position;        /* nvllm_layered_position: added to the scaled embedding */
+  int32_t tied_head;       /* 1: logits = embed x (the table itself, without embedding_scale); no "head" tensor */
+  float norm_offset;       /* norm weights are stored as w - norm_offset (1: "around zero") */
+  int32_t num_state_slots; /* recurrent mixers: sequences that can hold state at once (<= 0: max_num_seqs) */
 } nvllm_layered_config;
 
 int nvllm_create_layered(const nvllm_layered_config* cfg, const nvllm_layer_spec* layers,
@@ -229,6 +257,16 @@ int nvllm_set_named_weight(nvllm_handle* h, const char* name, int dtype, const v
  * sequence 1, ...).  After that run, nvllm_fetch_logits copies them out as [n_rows, V]. */
 int nvllm_request_logits(nvllm_handle* h, const int32_t* rows, int n_rows);
 int nvllm_fetch_logits(nvllm_handle* h, float* out, int n_rows);
+
+/* Models with recurrent mixers keep, per live sequence, a state slot (the recurrent state of
+ * every such layer and the last inputs of its short convolution).  The engine's cache manager
+ * hands slots out and takes them back like blocks; slots[i] in [0, num_state_slots) is the slot
+ * of sequence i of the NEXT nvllm_run, which reads the state when the sequence has cached
+ * tokens (num_cached > 0, or a decode step) and starts from zero otherwise, and leaves the
+ * state after the step's last token there.  Two sequences of a step must not share a slot.
+ * nvllm_state_slots reports how many slots the handle has (0: the model keeps no such state). */
+int nvllm_set_state_slots(nvllm_handle* h, const int32_t* slots, int n);
+int nvllm_state_slots(nvllm_handle* h);
 
 /* Hybrid models (ModelConfig.HybridLayers, config.go:113): types[l] = 1 makes layer l a Mamba2
  * block (norm -> Mamba2 -> residual, norm -> FFN -> residual; generic_model.go:162-202), 0 an
@@ -246,7 +284,8 @@ enum nvllm_arch {
   NVLLM_ARCH_FALCON = 1,      /* GetFalconMapping: fused query_key_value, parallel block */
   NVLLM_ARCH_LLAMA = 2,       /* GetLlamaMapping: separate q/k/v, gate_proj + up_proj */
   NVLLM_ARCH_GRANITE_MOE = 3, /* GetGraniteMoEMapping: router + stacked expert tensors */
-  NVLLM_ARCH_DUGOPEL = 4      /* layered handle: every tensor of the file by its own name */
+  NVLLM_ARCH_DUGOPEL = 4,     /* layered handle: every tensor of the file by its own name */
+  NVLLM_ARCH_ZOZONEX = 5      /* layered handle, likewise */
 };
 
 /* Load every weight of the model straight from `model_dir` — model.safetensors, or the shards
@@ -348,7 +387,8 @@ enum nvllm_kernel_class {
   NVLLM_K_SAMPLE = 12,
   NVLLM_K_MISC = 13,
   NVLLM_K_COMM = 14,        /* tensor-parallel partial sum + NCCL all-reduce / all-gather */
-  NVLLM_K_COUNT = 15
+  NVLLM_K_RECUR = 15,       /* recurrent mixers: short convolution, state scan, gated norm */
+  NVLLM_K_COUNT = 16
 };
 typedef struct nvllm_profile_entry {
   double ms;

@@ -26,9 +26,12 @@ ACT_GELU, ACT_SWIGLU = 0, 1
 BLOCK_SEQUENTIAL, BLOCK_PARALLEL = 0, 1
 PREC_FP32, PREC_BF16 = 0, 1
 # enum nvllm_arch (checkpoint families of generic_loader.go:60-182)
-ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL = 0, 1, 2, 3, 4
-MIXER_LATENT_ATTENTION = 1
+ARCH_GPT2, ARCH_FALCON, ARCH_LLAMA, ARCH_GRANITE_MOE, ARCH_DUGOPEL, ARCH_ZOZONEX = 0, 1, 2, 3, 4, 5
+MIXER_LATENT_ATTENTION, MIXER_WINDOW_ATTENTION, MIXER_DELTA = 1, 2, 3
 MLP_NONE, MLP_DENSE, MLP_MOE = 0, 1, 2
+FFN_GLU_CLAMPED, FFN_RELU2 = 0, 1
+LBLOCK_PARALLEL_PRENORM, LBLOCK_SEQUENTIAL_POSTNORM = 0, 1
+LPOS_NONE, LPOS_SINUSOIDAL = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 
 # enum nvllm_weight_id
@@ -297,6 +300,8 @@ class CLayerSpec(ctypes.Structure):
         ("experts", ctypes.c_int32), ("top", ctypes.c_int32),
         ("groups", ctypes.c_int32), ("keep_groups", ctypes.c_int32),
         ("router_scale", ctypes.c_float),
+        ("kv_heads", ctypes.c_int32), ("window", ctypes.c_int32), ("sink", ctypes.c_int32),
+        ("qk_norm", ctypes.c_int32), ("conv", ctypes.c_int32), ("act", ctypes.c_int32),
     ]
 
 
@@ -310,21 +315,24 @@ class CLayeredConfig(ctypes.Structure):
         ("precision", ctypes.c_int32), ("num_kv_blocks", ctypes.c_int32),
         ("max_num_seqs", ctypes.c_int32), ("max_batched_tokens", ctypes.c_int32),
         ("device", ctypes.c_int32),
+        ("block_style", ctypes.c_int32), ("position", ctypes.c_int32), ("tied_head", ctypes.c_int32),
+        ("norm_offset", ctypes.c_float), ("num_state_slots", ctypes.c_int32),
     ]
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a latent-attention mixer and its feed-forward (none, dense, or MoE)."""
+    """One layer: its mixer (latent attention, window attention or delta rule) and its
+    feed-forward (none, dense, or MoE)."""
     heads: int
     dim: int
-    rot_dim: int
     vdim: int
-    kv_rank: int
-    q_rank: int
-    rot_base: float
-    rot_dims: int
-    scale: float
+    rot_dim: int = 0
+    kv_rank: int = 0
+    q_rank: int = 0
+    rot_base: float = 0.0
+    rot_dims: int = 0
+    scale: float = 1.0
     kv_from: int = -1
     mixer: int = MIXER_LATENT_ATTENTION
     mlp: int = MLP_NONE
@@ -335,6 +343,12 @@ class LayerSpec:
     groups: int = 0
     keep_groups: int = 0
     router_scale: float = 1.0
+    kv_heads: int = 0
+    window: int = 0
+    sink: int = 0
+    qk_norm: int = 0
+    conv: int = 0
+    act: int = FFN_GLU_CLAMPED
 
     def to_c(self) -> CLayerSpec:
         c = CLayerSpec()
@@ -345,16 +359,34 @@ class LayerSpec:
     def tensor_shapes(self, layer: int, width: int) -> dict:
         """Checkpoint names and shapes of this layer's tensors (linears [out, in])."""
         p = f"l{layer}."
-        d = {p + "norm1": (width,),
-             p + "mix.dq": (self.q_rank, width), p + "mix.dq.norm": (self.q_rank,),
-             p + "mix.uq": (self.heads * (self.dim + self.rot_dim), self.q_rank),
-             p + "mix.uk": (self.heads * self.dim, self.kv_rank),
-             p + "mix.uv": (self.heads * self.vdim, self.kv_rank),
-             p + "mix.g": (self.heads, width), p + "mix.o": (width, self.heads * self.vdim)}
-        if self.kv_from < 0:
-            d[p + "mix.dkv"] = (self.kv_rank + self.rot_dim, width)
-            d[p + "mix.dkv.norm"] = (self.kv_rank,)
-        if self.mlp == MLP_DENSE:
+        if self.mixer == MIXER_WINDOW_ATTENTION:
+            d = {p + "norm1": (width,), p + "mix.q": (self.heads * self.dim, width),
+                 p + "mix.o": (width, self.heads * self.vdim)}
+            if self.kv_from < 0:
+                d[p + "mix.k"] = (self.kv_heads * self.dim, width)
+                d[p + "mix.v"] = (self.kv_heads * self.vdim, width)
+        elif self.mixer == MIXER_DELTA:
+            qk, v = self.kv_heads * self.dim, self.heads * self.vdim
+            d = {p + "norm1": (width,), p + "mix.q": (qk, width), p + "mix.k": (qk, width),
+                 p + "mix.v": (v, width), p + "mix.q.conv": (qk, self.conv),
+                 p + "mix.k.conv": (qk, self.conv), p + "mix.v.conv": (v, self.conv),
+                 p + "mix.b": (self.heads, width), p + "mix.a": (self.heads, width),
+                 p + "mix.A_log": (self.heads,), p + "mix.dt_bias": (self.heads,),
+                 p + "mix.norm": (self.vdim,), p + "mix.g": (v, width), p + "mix.o": (width, v)}
+        else:
+            d = {p + "norm1": (width,),
+                 p + "mix.dq": (self.q_rank, width), p + "mix.dq.norm": (self.q_rank,),
+                 p + "mix.uq": (self.heads * (self.dim + self.rot_dim), self.q_rank),
+                 p + "mix.uk": (self.heads * self.dim, self.kv_rank),
+                 p + "mix.uv": (self.heads * self.vdim, self.kv_rank),
+                 p + "mix.g": (self.heads, width), p + "mix.o": (width, self.heads * self.vdim)}
+            if self.kv_from < 0:
+                d[p + "mix.dkv"] = (self.kv_rank + self.rot_dim, width)
+                d[p + "mix.dkv.norm"] = (self.kv_rank,)
+        if self.mlp == MLP_DENSE and self.act == FFN_RELU2:
+            d.update({p + "norm2": (width,), p + "mlp.up": (self.ff, width),
+                      p + "mlp.down": (width, self.ff)})
+        elif self.mlp == MLP_DENSE:
             d.update({p + "mlp.gate": (self.ff, width), p + "mlp.up": (self.ff, width),
                       p + "mlp.down": (width, self.ff)})
         elif self.mlp == MLP_MOE:
@@ -367,7 +399,7 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class ListedModelConfig:
-    """A model whose config.json lists its layers (architecture "Dugopel")."""
+    """A model whose config.json lists its layers (architectures "Dugopel", "Zozonex")."""
     name: str
     vocab_size: int
     hidden: int
@@ -377,33 +409,57 @@ class ListedModelConfig:
     logit_softcap: float = 0.0
     eos_token_id: int = -1
     arch: int = ARCH_DUGOPEL
+    block_style: int = LBLOCK_PARALLEL_PRENORM
+    position: int = LPOS_NONE
+    tied_head: bool = False
+    norm_offset: float = 0.0
 
     @property
     def num_layers(self) -> int:
         return len(self.layers)
 
+    @property
+    def needs_state_slots(self) -> bool:
+        """True when some layer keeps recurrent state per sequence (delta rule)."""
+        return any(l.mixer == MIXER_DELTA for l in self.layers)
+
     def tensor_shapes(self) -> dict:
-        d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,),
-             "head": (self.vocab_size, self.hidden)}
+        d = {"embed": (self.vocab_size, self.hidden), "final.norm": (self.hidden,)}
+        if not self.tied_head:
+            d["head"] = (self.vocab_size, self.hidden)
         for i, l in enumerate(self.layers):
             d.update(l.tensor_shapes(i, self.hidden))
         return d
 
     def matmul_params(self) -> int:
-        return sum(a * b for (a, *r) in [s for s in self.tensor_shapes().values() if len(s) == 2]
-                   for b in r) - self.vocab_size * self.hidden
+        shapes = self.tensor_shapes()
+        n = sum(s[0] * s[1] for k, s in shapes.items() if len(s) == 2 and not k.endswith(".conv"))
+        return n - (0 if self.tied_head else self.vocab_size * self.hidden)
 
     def cache_bytes_per_token(self, bytes_per_el: int = 2) -> int:
-        return sum((l.kv_rank + l.rot_dim) * bytes_per_el for l in self.layers if l.kv_from < 0)
+        n = 0
+        for l in self.layers:
+            if l.mixer == MIXER_LATENT_ATTENTION and l.kv_from < 0:
+                n += (l.kv_rank + l.rot_dim) * bytes_per_el
+            elif l.mixer == MIXER_WINDOW_ATTENTION and l.kv_from < 0:
+                n += l.kv_heads * (l.dim + l.vdim) * bytes_per_el
+        return n
+
+    def state_bytes_per_sequence(self) -> int:
+        """fp32 recurrent state + convolution tail of the delta-rule layers."""
+        return sum(4 * (l.heads * l.dim * l.vdim + (l.conv - 1) * (2 * l.kv_heads * l.dim + l.heads * l.vdim))
+                   for l in self.layers if l.mixer == MIXER_DELTA)
 
     def to_c(self, precision: int, num_kv_blocks: int = -1, max_num_seqs: int = 512,
-             max_batched_tokens: int = 16384, device: int = 0):
+             max_batched_tokens: int = 16384, device: int = 0, num_state_slots: int = 0):
         c = CLayeredConfig()
         c.abi_version = ABI_VERSION
         c.vocab_size, c.hidden, c.num_layers = self.vocab_size, self.hidden, len(self.layers)
         c.norm_eps, c.embedding_scale, c.logit_softcap = self.norm_eps, self.embedding_scale, self.logit_softcap
         c.precision, c.num_kv_blocks = precision, num_kv_blocks
         c.max_num_seqs, c.max_batched_tokens, c.device = max_num_seqs, max_batched_tokens, device
+        c.block_style, c.position, c.tied_head = self.block_style, self.position, int(self.tied_head)
+        c.norm_offset, c.num_state_slots = self.norm_offset, num_state_slots
         specs = (CLayerSpec * len(self.layers))(*[l.to_c() for l in self.layers])
         return c, specs
 
@@ -441,8 +497,41 @@ def dugopel_from_json(j: dict) -> ListedModelConfig:
         logit_softcap=float(j.get("logit_softcap") or 0.0))
 
 
+def _zozonex_layer(i: int, lc: dict) -> LayerSpec:
+    m = lc["mixer"]
+    kind = lc.get("type")
+    kw = dict(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]))
+    if kind == "delta":
+        kw.update(mixer=MIXER_DELTA, conv=int(m["conv"]))
+    elif kind == "attention":
+        kw.update(mixer=MIXER_WINDOW_ATTENTION, scale=float(m["scale"]), window=int(m["mask"]["size"]),
+                  sink=1, qk_norm=1, kv_from=int(m["kv_from"]) if m.get("kv_from") is not None else -1)
+    else:
+        raise ValueError(f"layer {i}: unknown layer type {kind!r}")
+    mlp = lc.get("mlp")
+    if mlp is None:
+        pass
+    elif mlp["kind"] == "dense":
+        kw.update(mlp=MLP_DENSE, ff=int(mlp["ff"]), act=FFN_RELU2)
+    else:
+        raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+    return LayerSpec(**kw)
+
+
+def zozonex_from_json(j: dict) -> ListedModelConfig:
+    """config.json of the Zozonex design: delta-rule and sliding-window attention layers, each
+    sublayer followed by an RMS norm whose weight is stored around zero, sinusoidal positions
+    added to the scaled embedding, logits through the embedding table."""
+    return ListedModelConfig(
+        name="zozonex", vocab_size=int(j["vocab"]), hidden=int(j["width"]),
+        layers=tuple(_zozonex_layer(i, lc) for i, lc in enumerate(j["layers"])),
+        norm_eps=float(j["norm"]["eps"]), embedding_scale=float(j["embedding"]["scale"]),
+        arch=ARCH_ZOZONEX, block_style=LBLOCK_SEQUENTIAL_POSTNORM, position=LPOS_SINUSOIDAL,
+        tied_head=True, norm_offset=1.0)
+
+
 # model registry: config.json "architecture" -> config builder
-ARCHITECTURES = {"Dugopel": dugopel_from_json}
+ARCHITECTURES = {"Dugopel": dugopel_from_json, "Zozonex": zozonex_from_json}
 
 
 def from_model_dir(model_dir: str):

@@ -1,0 +1,585 @@
+// attention_window.cu — grouped-query attention over a sliding window of the paged K / V cache,
+// with an optional sink in the softmax, for the layers of a model given as a list
+// (nvllm_mixer_kind NVLLM_MIXER_WINDOW_ATTENTION).  Every size is a run-time argument.
+//
+//   q_h = norm(W_q x)_h, k_g = norm(W_k x)_g, v_g = (W_v x)_g      norm = x / sqrt(mean(x^2) + eps)
+//   s_ij = scale * q_i . k_j   for 0 <= i - j < window (window = 0: every j <= i)
+//   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij))                    sink = 1: a key of score 0 without a value
+//   o_i  = sum_j p_ij v_j;  query head h reads key / value head h / (H / G)
+//
+//  * winattn_prep_kernel: epilogue of the fused projection [Q | K | V] — split-K sum, the
+//    per-head norms, Q to the activation dtype, K / V rows into the layer's pools at slots[t]
+//    (pool layout [block][kv head][256][dim] and [...][vdim], addressed through the block tables
+//    like every other cache of the library).  A layer that borrows another layer's cache has no
+//    K / V columns and writes nothing.
+//  * winattn_kernel: fp32 arithmetic for any dim / vdim.  CTA = (query tile, head), 8 warps;
+//    a warp owns two queries of a 16-query sub-tile, its lanes own the keys of a 32-key tile for
+//    the scores and vdim / 32 output columns for the weighted sum.  Only the key tiles that a
+//    query of the sub-tile can see are read: [first query - window + 1, last query].  The sink
+//    is the initial state (max 0, denominator 1) of the running softmax.  Prefill steps come with
+//    a tile list; without one every sequence has one query at seq_len - 1 (decode).
+//  * winattn_mma_kernel (bf16, dim and vdim multiples of 16): the same on mma.sync m16n8k16,
+//    64 queries x one head per CTA, K / V tiles of 64 keys by cp.async (double buffered).
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "mma.cuh"
+
+namespace nvllm {
+
+namespace {
+__device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, size_t stride) {
+  float acc = 0.f;
+  for (int s = 0; s < S; s++) acc += p[(size_t)s * stride];
+  return acc;
+}
+}  // namespace
+
+// ------------------------------------------------------------------ projection epilogue
+// grid (T), 256 threads; warps take the heads of the row in turn: H query heads, then (own
+// cache only) G key heads and G value heads
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int n_items = a.H + (a.own_kv ? 2 * a.G : 0);
+  const float* row = a.in_p + (size_t)t * a.in_ld;
+  const int slot = a.slots[t];
+  const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
+  for (int it = warp; it < n_items; it += nw) {
+    int col, n, kind;  // 0 = query, 1 = key, 2 = value
+    if (it < a.H) { kind = 0; n = a.dim; col = it * a.dim; }
+    else if (it < a.H + a.G) { kind = 1; n = a.dim; col = a.H * a.dim + (it - a.H) * a.dim; }
+    else { kind = 2; n = a.vdim; col = (a.H + a.G) * a.dim + (it - a.H - a.G) * a.vdim; }
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float v = sum_slices(row + col + i, a.in_S, a.in_stride);
+      ss += v * v;
+    }
+    float inv = 1.f;
+    if (kind != 2 && a.qk_norm) inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + a.eps);
+    if (kind == 0) {
+      QT* dst = (QT*)a.q + (size_t)t * a.H * a.dim + col;
+      for (int i = lane; i < n; i += 32) dst[i] = from_f32<QT>(sum_slices(row + col + i, a.in_S, a.in_stride) * inv);
+    } else if (kind == 1) {
+      const int g = it - a.H;
+      KT* dst = (KT*)a.kpool + (((size_t)blk * a.G + g) * KV_BLOCK + off) * a.dim;
+      for (int i = lane; i < n; i += 32) dst[i] = from_f32<KT>(sum_slices(row + col + i, a.in_S, a.in_stride) * inv);
+    } else {
+      const int g = it - a.H - a.G;
+      KT* dst = (KT*)a.vpool + (((size_t)blk * a.G + g) * KV_BLOCK + off) * a.vdim;
+      for (int i = lane; i < n; i += 32) dst[i] = from_f32<KT>(sum_slices(row + col + i, a.in_S, a.in_stride));
+    }
+  }
+  TRACE_EXIT(tr);
+}
+
+cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a) {
+  if (a.T <= 0) return cudaSuccess;
+  if (qdt == DT_F32 && kvdt == DT_F32)
+    (void)launch_k(winattn_prep_kernel<float, float>, dim3(a.T), dim3(256), 0, st, a, next_trace(30));
+  else if (qdt == DT_BF16 && kvdt == DT_BF16)
+    (void)launch_k(winattn_prep_kernel<bf16, bf16>, dim3(a.T), dim3(256), 0, st, a, next_trace(30));
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ attention, fp32 arithmetic
+constexpr int WA_KT = 32;  // keys per tile (divides KV_BLOCK)
+constexpr int WA_QS = 16;  // queries per sub-tile: 8 warps x 2
+
+template <typename QT, typename KT, int VPL>
+__global__ void __launch_bounds__(256) winattn_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float smem[];
+  const int dim = a.dim, vdim = a.vdim;
+  const int kld = dim | 1;  // odd row stride: the 32 lanes read 32 different banks
+  float* Qs = smem;                   // [WA_QS][dim], scaled
+  float* Ks = Qs + WA_QS * dim;       // [WA_KT][kld]
+  float* Vs = Ks + WA_KT * kld;       // [WA_KT][vdim]
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int seq, q0, n_new, row0, qpos0;
+  if (a.tile_seq) {
+    seq = a.tile_seq[tile];
+    q0 = a.tile_q0[tile];
+    n_new = a.cu_q[seq + 1] - a.cu_q[seq];
+    row0 = a.cu_q[seq] + q0;
+    qpos0 = a.seq_start[seq] + q0;
+  } else {
+    seq = tile; q0 = 0; n_new = 1; row0 = seq;
+    qpos0 = a.seq_len[seq] - 1;
+  }
+  const int nq = min(a.qtile, n_new - q0);
+  const int g = head / (a.H / a.G);
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const KT* kpool = (const KT*)a.kpool;
+  const KT* vpool = (const KT*)a.vpool;
+  const float m0 = a.sink ? 0.f : -INFINITY, l0 = a.sink ? 1.f : 0.f;
+
+  for (int qb = 0; qb < nq; qb += WA_QS) {
+    const int nqs = min(WA_QS, nq - qb);
+    __syncthreads();  // the previous sub-tile's Qs / Ks / Vs have been consumed
+    for (int i = threadIdx.x; i < nqs * dim; i += blockDim.x) {
+      const int qi = i / dim, d = i % dim;
+      Qs[i] = to_f32(((const QT*)a.q)[(size_t)(row0 + qb + qi) * a.H * dim + head * dim + d]) * a.scale;
+    }
+    float m[2], l[2], acc[2][VPL];
+#pragma unroll
+    for (int qq = 0; qq < 2; qq++) {
+      m[qq] = m0;
+      l[qq] = l0;
+#pragma unroll
+      for (int c = 0; c < VPL; c++) acc[qq][c] = 0.f;
+    }
+    const int p_first = qpos0 + qb, p_last = qpos0 + qb + nqs - 1;
+    int k_lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    k_lo = k_lo / WA_KT * WA_KT;
+    const int k_hi = p_last + 1;
+    for (int k0 = k_lo; k0 < k_hi; k0 += WA_KT) {
+      const int nk = min(WA_KT, k_hi - k0);
+      const int blk = bt[k0 / KV_BLOCK];
+      const size_t kb = (((size_t)blk * a.G + g) * KV_BLOCK + (k0 % KV_BLOCK));
+      __syncthreads();
+      for (int i = threadIdx.x; i < nk * dim; i += blockDim.x) {
+        const int r = i / dim, d = i % dim;
+        Ks[r * kld + d] = to_f32(kpool[(kb + r) * dim + d]);
+      }
+      for (int i = threadIdx.x; i < nk * vdim; i += blockDim.x) Vs[i] = to_f32(vpool[kb * vdim + i]);
+      __syncthreads();
+#pragma unroll
+      for (int qq = 0; qq < 2; qq++) {
+        const int qi = warp + 8 * qq;
+        if (qi >= nqs) continue;  // warp-uniform
+        const int qp = p_first + qi;
+        const int j = k0 + lane;
+        const bool vis = lane < nk && j <= qp && (a.window <= 0 || qp - j < a.window);
+        float s = -INFINITY;
+        if (vis) {
+          const float* qr = Qs + qi * dim;
+          const float* kr = Ks + lane * kld;
+          float d = 0.f;
+          for (int i = 0; i < dim; i++) d = fmaf(qr[i], kr[i], d);
+          s = d;
+        }
+        const float cmax = warp_max(s);
+        if (cmax == -INFINITY) continue;  // no key of this tile is visible to the query
+        const float mn = fmaxf(m[qq], cmax);
+        const float corr = (m[qq] == -INFINITY) ? 0.f : expf(m[qq] - mn);
+        const float p = vis ? expf(s - mn) : 0.f;
+        l[qq] = l[qq] * corr + warp_sum(p);
+#pragma unroll
+        for (int c = 0; c < VPL; c++) acc[qq][c] *= corr;
+        for (int jj = 0; jj < nk; jj++) {
+          const float pj = __shfl_sync(0xffffffffu, p, jj);
+          if (pj == 0.f) continue;  // warp-uniform
+          const float* vr = Vs + jj * vdim;
+#pragma unroll
+          for (int c = 0; c < VPL; c++) {
+            const int col = lane + 32 * c;
+            if (col < vdim) acc[qq][c] = fmaf(pj, vr[col], acc[qq][c]);
+          }
+        }
+        m[qq] = mn;
+      }
+    }
+#pragma unroll
+    for (int qq = 0; qq < 2; qq++) {
+      const int qi = warp + 8 * qq;
+      if (qi >= nqs) continue;
+      const float inv = 1.0f / l[qq];
+      QT* op = (QT*)a.out + (size_t)(row0 + qb + qi) * a.o_ld;
+#pragma unroll
+      for (int c = 0; c < VPL; c++) {
+        const int col = lane + 32 * c;
+        if (col < vdim) op[head * vdim + col] = from_f32<QT>(acc[qq][c] * inv);
+      }
+      if (head == 0)  // padding columns of the output projection's input stay zero
+        for (int col = a.H * vdim + lane; col < a.o_ld; col += 32) op[col] = from_f32<QT>(0.f);
+    }
+  }
+  TRACE_EXIT(tr);
+}
+
+template <typename QT, typename KT>
+static cudaError_t winattn_dispatch(cudaStream_t st, const WinAttnArgs& a) {
+  const dim3 grid(a.n_tiles, a.H);
+  const size_t smem = ((size_t)WA_QS * a.dim + (size_t)WA_KT * (a.dim | 1) + (size_t)WA_KT * a.vdim) * sizeof(float);
+  const int vpl = ceil_div(a.vdim, 32);
+#define WA(V)                                                                                               \
+  {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                   \
+      cudaFuncSetAttribute(winattn_kernel<QT, KT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    (void)launch_k(winattn_kernel<QT, KT, V>, grid, dim3(256), smem, st, a, next_trace(31));                \
+  }
+  if (vpl <= 1) WA(1)
+  else if (vpl <= 2) WA(2)
+  else if (vpl <= 4) WA(4)
+  else if (vpl <= 8) WA(8)
+  else if (vpl <= 16) WA(16)
+  else return cudaErrorInvalidValue;
+#undef WA
+  return cudaGetLastError();
+}
+
+
+// ------------------------------------------------------------------ decode: one query per sequence
+// CTA = (sequence, head), 4 warps that take the window's 32-key chunks in turn: a lane scores
+// its own key (a cached row is contiguous), the chunk's probabilities are then broadcast lane
+// by lane for the weighted sum over the value rows (coalesced); the four partial states meet in
+// shared memory, where the sink joins once.
+template <typename QT, typename KT, int VPL>
+__global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float smem[];
+  const int dim = a.dim, vdim = a.vdim;
+  float* qs = smem;             // [dim], scaled
+  float* part = smem + dim;     // [4][vdim + 2]
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = head / (a.H / a.G);
+  const int qp = a.seq_len[seq] - 1;
+  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const KT* kpool = (const KT*)a.kpool;
+  const KT* vpool = (const KT*)a.vpool;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x)
+    qs[i] = to_f32(((const QT*)a.q)[(size_t)seq * a.H * dim + head * dim + i]) * a.scale;
+  __syncthreads();
+  float m = -INFINITY, l = 0.f, acc[VPL];
+#pragma unroll
+  for (int c = 0; c < VPL; c++) acc[c] = 0.f;
+  for (int k0 = k_lo + warp * 32; k0 <= qp; k0 += 4 * 32) {
+    const int j = k0 + lane;
+    const bool vis = j <= qp;
+    float s = -INFINITY;
+    if (vis) {
+      const KT* kr = kpool + (((size_t)bt[j / KV_BLOCK] * a.G + g) * KV_BLOCK + (j % KV_BLOCK)) * dim;
+      float d = 0.f;
+      for (int i = 0; i < dim; i++) d = fmaf(qs[i], to_f32(kr[i]), d);
+      s = d;
+    }
+    const float mn = fmaxf(m, warp_max(s));  // lane 0 of the chunk is always visible
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - mn);
+    const float p = vis ? expf(s - mn) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int c = 0; c < VPL; c++) acc[c] *= corr;
+    const int nk = min(32, qp + 1 - k0);
+    for (int jj = 0; jj < nk; jj++) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const int jp = k0 + jj;
+      const KT* vr = vpool + (((size_t)bt[jp / KV_BLOCK] * a.G + g) * KV_BLOCK + (jp % KV_BLOCK)) * vdim;
+#pragma unroll
+      for (int c = 0; c < VPL; c++) {
+        const int col = lane + 32 * c;
+        if (col < vdim) acc[c] = fmaf(pj, to_f32(vr[col]), acc[c]);
+      }
+    }
+    m = mn;
+  }
+  float* mine = part + warp * (vdim + 2);
+#pragma unroll
+  for (int c = 0; c < VPL; c++) {
+    const int col = lane + 32 * c;
+    if (col < vdim) mine[col] = acc[c];
+  }
+  if (lane == 0) {
+    mine[vdim] = m;
+    mine[vdim + 1] = l;
+  }
+  __syncthreads();
+  float mt = a.sink ? 0.f : -INFINITY;
+  for (int w = 0; w < 4; w++) mt = fmaxf(mt, part[w * (vdim + 2) + vdim]);
+  float lt = a.sink ? expf(0.f - mt) : 0.f;
+  float cw[4];
+  for (int w = 0; w < 4; w++) {
+    const float mw = part[w * (vdim + 2) + vdim];
+    cw[w] = (mw == -INFINITY) ? 0.f : expf(mw - mt);
+    lt += part[w * (vdim + 2) + vdim + 1] * cw[w];
+  }
+  QT* op = (QT*)a.out + (size_t)seq * a.o_ld;
+  for (int col = threadIdx.x; col < vdim; col += blockDim.x) {
+    float v = 0.f;
+    for (int w = 0; w < 4; w++) v += part[w * (vdim + 2) + col] * cw[w];
+    op[head * vdim + col] = from_f32<QT>(v / lt);
+  }
+  if (head == 0)
+    for (int col = a.H * vdim + threadIdx.x; col < a.o_ld; col += blockDim.x) op[col] = from_f32<QT>(0.f);
+  TRACE_EXIT(tr);
+}
+
+template <typename QT, typename KT>
+static cudaError_t winattn_decode_dispatch(cudaStream_t st, const WinAttnArgs& a) {
+  const dim3 grid(a.n_tiles, a.H);
+  const size_t smem = ((size_t)a.dim + 4 * ((size_t)a.vdim + 2)) * sizeof(float);
+  const int vpl = ceil_div(a.vdim, 32);
+#define WD(V) (void)launch_k(winattn_decode_kernel<QT, KT, V>, grid, dim3(128), smem, st, a, next_trace(33));
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  if (vpl <= 1) WD(1)
+  else if (vpl <= 2) WD(2)
+  else if (vpl <= 4) WD(4)
+  else if (vpl <= 8) WD(8)
+  else if (vpl <= 16) WD(16)
+  else return cudaErrorInvalidValue;
+#undef WD
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ attention on mma.sync (bf16)
+// CTA = 64 queries of one sequence x one head, 4 warps x 16 query rows.  Q [64][DP] and the K / V
+// tiles [64][DP] / [64][VP] live in shared memory with rows padded by 8 elements (ldmatrix
+// without bank conflicts); DP / VP = dim / vdim (multiples of 16).  S = Q K^T in fp32
+// accumulators, masked per element (causal + window), online softmax in the accumulator layout
+// (the sink is the initial max 0 / denominator 1), P rounded to bf16 as the A operand of O += P V
+// with V read through ldmatrix.trans.  Key tiles outside [first query - window + 1, last query]
+// are never loaded; K / V of tile i + 1 arrive by cp.async while tile i is computed.
+constexpr int WM_Q = 64, WM_K = 64;
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int DP = DIM + 8, VP = VDIM + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [64][DP]
+  bf16* Ks = Qs + WM_Q * DP;                      // [2][64][DP]
+  bf16* Vs = Ks + 2 * WM_K * DP;                  // [2][64][VP]
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int seq, q0, n_new, row0, qpos0;
+  if (a.tile_seq) {
+    seq = a.tile_seq[tile];
+    q0 = a.tile_q0[tile];
+    n_new = a.cu_q[seq + 1] - a.cu_q[seq];
+    row0 = a.cu_q[seq] + q0;
+    qpos0 = a.seq_start[seq] + q0;
+  } else {
+    seq = tile; q0 = 0; n_new = 1; row0 = seq;
+    qpos0 = a.seq_len[seq] - 1;
+  }
+  const int nq = min(WM_Q, n_new - q0);
+  const int g = head / (a.H / a.G);
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const bf16* kpool = (const bf16*)a.kpool;
+  const bf16* vpool = (const bf16*)a.vpool;
+  const bf16* qg = (const bf16*)a.q + (size_t)row0 * a.H * DIM + head * DIM;
+
+  // Q tile: rows past nq are zero
+  for (int i = threadIdx.x; i < WM_Q * (DIM / 8); i += blockDim.x) {
+    const int r = i / (DIM / 8), c = i % (DIM / 8);
+    const bool ok = r < nq;
+    cp_async16(smem_addr(Qs + r * DP + c * 8), ok ? (const void*)(qg + (size_t)r * a.H * DIM + c * 8) : (const void*)qg, ok);
+  }
+  int k_lo = a.window > 0 ? max(0, qpos0 - a.window + 1) : 0;
+  k_lo = k_lo / WM_K * WM_K;
+  const int k_hi = qpos0 + nq;  // keys [k_lo, k_hi)
+  const int n_kt = (k_hi - k_lo + WM_K - 1) / WM_K;
+  auto load_kv = [&](int kt, int buf) {
+    const int k0 = k_lo + kt * WM_K;
+    const int nk = min(WM_K, k_hi - k0);
+    const int blk = bt[k0 / KV_BLOCK];
+    const size_t kb = (((size_t)blk * a.G + g) * KV_BLOCK + (k0 % KV_BLOCK));
+    bf16* kd = Ks + buf * WM_K * DP;
+    bf16* vd = Vs + buf * WM_K * VP;
+    for (int i = threadIdx.x; i < WM_K * (DIM / 8); i += blockDim.x) {
+      const int r = i / (DIM / 8), c = i % (DIM / 8);
+      const bool ok = r < nk;
+      cp_async16(smem_addr(kd + r * DP + c * 8), ok ? (const void*)(kpool + (kb + r) * DIM + c * 8) : (const void*)kpool, ok);
+    }
+    for (int i = threadIdx.x; i < WM_K * (VDIM / 8); i += blockDim.x) {
+      const int r = i / (VDIM / 8), c = i % (VDIM / 8);
+      const bool ok = r < nk;
+      cp_async16(smem_addr(vd + r * VP + c * 8), ok ? (const void*)(vpool + (kb + r) * VDIM + c * 8) : (const void*)vpool, ok);
+    }
+  };
+  load_kv(0, 0);
+  cp_async_commit();
+
+  const int gid = lane >> 2, tig = lane & 3;
+  const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;     // the thread's two query rows in the tile
+  const int qp_lo = qpos0 + r_lo, qp_hi = qpos0 + r_hi;  // their positions
+  float m_lo, m_hi, l_lo, l_hi;
+  m_lo = m_hi = a.sink ? 0.f : -INFINITY;
+  l_lo = l_hi = a.sink ? 1.f : 0.f;
+  float o[VDIM / 8][4];
+#pragma unroll
+  for (int i = 0; i < VDIM / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float sc = a.scale;
+
+  for (int kt = 0; kt < n_kt; kt++) {
+    const int buf = kt & 1;
+    if (kt + 1 < n_kt) load_kv(kt + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int k0 = k_lo + kt * WM_K;
+    const bf16* kd = Ks + buf * WM_K * DP;
+    const bf16* vd = Vs + buf * WM_K * VP;
+    // does any row of this warp see any key of the tile?
+    const int w_qlo = qpos0 + warp * 16, w_qhi = w_qlo + 15;
+    const bool warp_sees = warp * 16 < nq && k0 <= w_qhi && (a.window <= 0 || k0 + WM_K - 1 > w_qlo - a.window);
+    if (warp_sees) {
+      float s[WM_K / 8][4];
+#pragma unroll
+      for (int i = 0; i < WM_K / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DIM / 16; kk++) {
+        uint32_t a0, a1, a2, a3;
+        // A fragment (16 query rows x 16 dims): matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7),
+        // (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+        ldsm_x4(smem_addr(Qs + (warp * 16 + (lane & 15)) * DP + kk * 16 + (lane >> 4) * 8), a0, a1, a2, a3);
+#pragma unroll
+        for (int nb = 0; nb < WM_K / 16; nb++) {
+          // B fragments of two 8-key blocks: K rows are the n index, dims the k index
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(smem_addr(kd + (nb * 16 + (lane & 7) + ((lane >> 4) << 3)) * DP + kk * 16 + ((lane >> 3) & 1) * 8),
+                  b0, b1, b2, b3);
+          mma16816(s[2 * nb], a0, a1, a2, a3, b0, b1);
+          mma16816(s[2 * nb + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      // scale, mask, running max
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < WM_K / 8; nb++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int j = k0 + nb * 8 + tig * 2 + (e & 1);
+          const int qp = (e & 2) ? qp_hi : qp_lo;
+          const bool vis = j <= qp && j < k_hi && (a.window <= 0 || qp - j < a.window);
+          const float v = vis ? s[nb][e] * sc : -INFINITY;
+          s[nb][e] = v;
+          if (e & 2) mx_hi = fmaxf(mx_hi, v);
+          else mx_lo = fmaxf(mx_lo, v);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      // a row that has seen nothing yet (and has no sink) keeps max -inf: every p below is 0
+      const float c_lo = (mn_lo == -INFINITY) ? 1.f : ((m_lo == -INFINITY) ? 0.f : expf(m_lo - mn_lo));
+      const float c_hi = (mn_hi == -INFINITY) ? 1.f : ((m_hi == -INFINITY) ? 0.f : expf(m_hi - mn_hi));
+      float ps_lo = 0.f, ps_hi = 0.f;
+      uint32_t pa[WM_K / 8][2];
+#pragma unroll
+      for (int nb = 0; nb < WM_K / 8; nb++) {
+        const float p0 = (s[nb][0] == -INFINITY) ? 0.f : expf(s[nb][0] - mn_lo);
+        const float p1 = (s[nb][1] == -INFINITY) ? 0.f : expf(s[nb][1] - mn_lo);
+        const float p2 = (s[nb][2] == -INFINITY) ? 0.f : expf(s[nb][2] - mn_hi);
+        const float p3 = (s[nb][3] == -INFINITY) ? 0.f : expf(s[nb][3] - mn_hi);
+        ps_lo += p0 + p1;
+        ps_hi += p2 + p3;
+        pa[nb][0] = pack_bf16(p0, p1);
+        pa[nb][1] = pack_bf16(p2, p3);
+      }
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
+      l_lo = l_lo * c_lo + ps_lo;
+      l_hi = l_hi * c_hi + ps_hi;
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) {
+        o[i][0] *= c_lo; o[i][1] *= c_lo;
+        o[i][2] *= c_hi; o[i][3] *= c_hi;
+      }
+      // O += P V: P (16 x 64 keys) as A fragments of 16 keys each, V [key][vdim] through ldmatrix.trans
+#pragma unroll
+      for (int kk = 0; kk < WM_K / 16; kk++) {
+        const uint32_t a0 = pa[2 * kk][0], a1 = pa[2 * kk][1], a2 = pa[2 * kk + 1][0], a3 = pa[2 * kk + 1][1];
+#pragma unroll
+        for (int nb = 0; nb < VDIM / 16; nb++) {
+          uint32_t b0, b1, b2, b3;
+          // matrices: (keys 0-7, cols 0-7), (keys 8-15, cols 0-7), (keys 0-7, cols 8-15), (keys 8-15, cols 8-15)
+          ldsm_x4_t(smem_addr(vd + (kk * 16 + (lane & 15)) * VP + nb * 16 + (lane >> 4) * 8), b0, b1, b2, b3);
+          mma16816(o[2 * nb], a0, a1, a2, a3, b0, b1);
+          mma16816(o[2 * nb + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // the buffer is free for the load of tile kt + 2
+  }
+  cp_async_wait<0>();
+  const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
+  bf16* ob = (bf16*)a.out + (size_t)row0 * a.o_ld + head * VDIM;
+#pragma unroll
+  for (int i = 0; i < VDIM / 8; i++) {
+    const int col = i * 8 + tig * 2;
+    if (r_lo < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_lo * a.o_ld + col) = pack_bf16(o[i][0] * i_lo, o[i][1] * i_lo);
+    if (r_hi < nq) *reinterpret_cast<uint32_t*>(ob + (size_t)r_hi * a.o_ld + col) = pack_bf16(o[i][2] * i_hi, o[i][3] * i_hi);
+  }
+  if (head == 0) {
+    bf16* orow = (bf16*)a.out + (size_t)row0 * a.o_ld;
+    const int pad = a.o_ld - a.H * VDIM;
+    for (int i = threadIdx.x; i < nq * pad; i += blockDim.x)
+      orow[(size_t)(i / pad) * a.o_ld + a.H * VDIM + i % pad] = __float2bfloat16_rn(0.f);
+  }
+  TRACE_EXIT(tr);
+}
+
+static bool winattn_mma_on() {
+  static const bool on = [] {
+    const char* e = getenv("NVLLM_WINATTN_MMA");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return on;
+}
+// compile-time (dim, vdim) pairs of the mma.sync kernel
+static bool winattn_mma_shape(int dim, int vdim) {
+  return (dim == 64 && vdim == 64) || (dim == 96 && vdim == 96) || (dim == 128 && vdim == 128) ||
+         (dim == 32 && vdim == 32) || (dim == 64 && vdim == 128) || (dim == 128 && vdim == 64);
+}
+bool winattn_uses_mma(int qdt, int kvdt, int dim, int vdim) {
+  return winattn_mma_on() && qdt == DT_BF16 && kvdt == DT_BF16 && winattn_mma_shape(dim, vdim);
+}
+int winattn_qtile(int qdt, int kvdt, int dim, int vdim) {
+  return winattn_uses_mma(qdt, kvdt, dim, vdim) ? WM_Q : WA_QS;
+}
+
+template <int DIM, int VDIM>
+static cudaError_t winattn_mma_launch(cudaStream_t st, const WinAttnArgs& a) {
+  const size_t smem = ((size_t)WM_Q * (DIM + 8) + 2 * (size_t)WM_K * (DIM + 8) + 2 * (size_t)WM_K * (VDIM + 8)) * 2;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(winattn_mma_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  (void)launch_k(winattn_mma_kernel<DIM, VDIM>, dim3(a.n_tiles, a.H), dim3(128), smem, st, a, next_trace(32));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_winattn(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a) {
+  if (a.n_tiles <= 0) return cudaSuccess;
+  if (a.H % a.G) return cudaErrorInvalidValue;
+  if (a.tile_seq == nullptr) {  // decode: one query per sequence
+    if (qdt == DT_F32 && kvdt == DT_F32) return winattn_decode_dispatch<float, float>(st, a);
+    if (qdt == DT_BF16 && kvdt == DT_BF16) return winattn_decode_dispatch<bf16, bf16>(st, a);
+    return cudaErrorInvalidValue;
+  }
+  // the mma kernel's tile is 64 queries: prefill steps whose tile list was built for it
+  if (winattn_uses_mma(qdt, kvdt, a.dim, a.vdim) && a.qtile == WM_Q && (a.o_ld % 2) == 0) {
+    if (a.dim == 64 && a.vdim == 64) return winattn_mma_launch<64, 64>(st, a);
+    if (a.dim == 96 && a.vdim == 96) return winattn_mma_launch<96, 96>(st, a);
+    if (a.dim == 128 && a.vdim == 128) return winattn_mma_launch<128, 128>(st, a);
+    if (a.dim == 32 && a.vdim == 32) return winattn_mma_launch<32, 32>(st, a);
+    if (a.dim == 64 && a.vdim == 128) return winattn_mma_launch<64, 128>(st, a);
+    if (a.dim == 128 && a.vdim == 64) return winattn_mma_launch<128, 64>(st, a);
+  }
+  if (qdt == DT_F32 && kvdt == DT_F32) return winattn_dispatch<float, float>(st, a);
+  if (qdt == DT_BF16 && kvdt == DT_BF16) return winattn_dispatch<bf16, bf16>(st, a);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace nvllm

@@ -87,6 +87,10 @@ __device__ __forceinline__ float gelu_tanh(float x) {  // tensor.go:181-190
   float inner = 0.7978845608028654f * (x + 0.044715f * x3);
   return 0.5f * x * (1.0f + tanhf(inner));
 }
+__device__ __forceinline__ float relu2(float x) {
+  const float r = fmaxf(x, 0.f);
+  return r * r;
+}
 __device__ __forceinline__ float silu(float x) {  // mamba2.go:360-367
   return x / (1.0f + expf(-x));
 }

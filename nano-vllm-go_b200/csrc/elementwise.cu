@@ -16,7 +16,8 @@ template <typename WT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const WT* __restrict__ wte, const WT* __restrict__ wpe, int max_pos,
                              float mult, float* __restrict__ x, int H, bf16* __restrict__ xb,
-                             float* __restrict__ ssq, const float* __restrict__ g, Trace tr) {
+                             float* __restrict__ ssq, const float* __restrict__ g,
+                             const double* __restrict__ pos_freq, WT* __restrict__ y, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_wait();  // step prologue: later kernels may read the step state before their own wait
   pdl_launch_dependents();
@@ -41,7 +42,18 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
 #pragma unroll
       for (int j = 0; j < 8; j++) v[j] *= mult;
     }
+    if (pos_freq) {
+      // sinusoidal positions: entries (2k, 2k + 1) get sin / cos of pos * pos_freq[k]
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        double sn, cs;
+        sincos((double)pos * pos_freq[(i + j) >> 1], &sn, &cs);
+        v[j] += (float)sn;
+        v[j + 1] += (float)cs;
+      }
+    }
     store8(x + (size_t)t * H + i, v);
+    if (y) store8(y + (size_t)t * H + i, v);
     if (xb) {
       float gv[8], o[8];
       load8(g + i, gv);
@@ -62,16 +74,16 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
 
 cudaError_t launch_embed(cudaStream_t st, int wdt, const int* tokens, const int* positions,
                          const void* wte, const void* wpe, int max_pos, float mult, float* x, int T,
-                         int H, void* xb, float* ssq, const float* g) {
+                         int H, void* xb, float* ssq, const float* g, const double* pos_freq, void* y) {
   if (T <= 0) return cudaSuccess;
   if ((xb == nullptr) != (ssq == nullptr) || (xb && !g)) return cudaErrorInvalidValue;
   int threads = min(256, max(32, ((H / 8 + 31) / 32) * 32));
   if (wdt == DT_F32)
     (void)launch_k(embed_kernel<float>, dim3(T), dim3(threads), 0, st, tokens, positions, (const float*)wte,
-                                               (const float*)wpe, max_pos, mult, x, H, (bf16*)xb, ssq, g, next_trace(5));
+                                               (const float*)wpe, max_pos, mult, x, H, (bf16*)xb, ssq, g, pos_freq, (float*)y, next_trace(5));
   else
     (void)launch_k(embed_kernel<bf16>, dim3(T), dim3(threads), 0, st, tokens, positions, (const bf16*)wte,
-                                              (const bf16*)wpe, max_pos, mult, x, H, (bf16*)xb, ssq, g, next_trace(5));
+                                              (const bf16*)wpe, max_pos, mult, x, H, (bf16*)xb, ssq, g, pos_freq, (bf16*)y, next_trace(5));
   return cudaGetLastError();
 }
 
@@ -94,7 +106,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
 #pragma unroll
   for (int j = 0; j < 8; j++) w0[j] = b0[j] = bias1_0[j] = bias2_0[j] = 0.f;
   if (i0 < H) {
-    if (a.y) {
+    if (a.y || a.post) {
       if (a.w) load8(a.w + i0, w0);
       else
 #pragma unroll
@@ -109,6 +121,34 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
   const int orow = blockIdx.x;
   const int r = a.row_idx ? a.row_idx[orow] - a.row_bias : orow;
   float* xr = a.x + (size_t)r * H;
+  if (a.post) {
+    // the norm sits on the addend: x <- x + rmsnorm(sum_s p1[s]) * w; y = x in the act dtype
+    float lsq = 0.f;
+    for (int i = i0; i < H; i += blockDim.x * 8) {
+      float acc[8];
+      sum_partials8(a.p1 + (size_t)r * H + i, a.S1, a.stride1, acc);
+      store8(row + i, acc);
+#pragma unroll
+      for (int j = 0; j < 8; j++) lsq += acc[j] * acc[j];
+    }
+    const float inv = 1.0f / sqrtf(block_sum(lsq, red) / (float)H + a.eps);
+    YT* yr = a.y ? (YT*)a.y + (size_t)orow * H : nullptr;
+    for (int i = i0; i < H; i += blockDim.x * 8) {
+      float v[8], w[8];
+      load8(xr + i, v);
+      if (i == i0) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) w[j] = w0[j];
+      } else {
+        load8(a.w + i, w);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = fmaf(row[i + j] * inv, w[j], v[j]);
+      store8(xr + i, v);
+      if (yr) store8(yr + i, v);
+    }
+    return;
+  }
   const bool upd = (a.p1 != nullptr) || (a.p2 != nullptr);
   const bool ln = a.b != nullptr || a.centered != 0;  // LayerNorm (with or without the additive term)
   float lsum = 0.f;
@@ -270,6 +310,8 @@ __global__ void act_kernel(int T, int F, const float* __restrict__ h, int S, siz
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
+  const int act2 = swiglu == 2;  // squared ReLU: a plain (ungated) activation
+  if (act2) swiglu = 0;
   const int ld = swiglu ? 2 * F : F;
   const size_t nvec = (size_t)T * (F / 8);
   for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
@@ -314,7 +356,7 @@ __global__ void act_kernel(int T, int F, const float* __restrict__ h, int S, siz
         for (int i = 0; i < 8; i++) g[i] += p[i];
       }
 #pragma unroll
-      for (int i = 0; i < 8; i++) o[i] = gelu_tanh(g[i]);
+      for (int i = 0; i < 8; i++) o[i] = act2 ? relu2(g[i]) : gelu_tanh(g[i]);
     }
     store8(out + (size_t)t * F + j, o);
   }

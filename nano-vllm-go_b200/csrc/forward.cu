@@ -24,7 +24,7 @@ void free_workspace(nvllm_handle* h) {
   Workspace& w = h->ws;
   h->drop_graphs();  // the captured decode steps hold these pointers
   void* ptrs[] = {w.tp_buf, w.x, w.xn, w.xn_f32, w.ws_a, w.ws_b, w.ws_c, w.q, w.attn_out, w.hbuf, w.xn_last,
-                  w.xb, w.ssq, w.chain_ctr, w.lat_cq, w.lat_gate, w.lat_o, w.m_xbc, w.m_dt, w.m_y, w.m_yn, w.logits_p, w.logits, w.attn_ws, w.out_tokens, w.amax, w.amax_ticket, w.topk_idx, w.topk_w,
+                  w.xb, w.ssq, w.chain_ctr, w.lat_cq, w.lat_gate, w.lat_o, w.dl_qkv, w.dl_bg, w.dl_o, w.m_xbc, w.m_dt, w.m_y, w.m_yn, w.logits_p, w.logits, w.attn_ws, w.out_tokens, w.amax, w.amax_ticket, w.topk_idx, w.topk_w,
                   w.sort.counts, w.sort.offsets, w.sort.cursor, w.sort.sorted_pair, w.sort.pair_row,
                   w.sort.a_rows, w.sort.tile_expert, w.sort.tile_row0, w.sort.tile_rows,
                   w.sort.n_tiles, w.moe_Y, w.moe_y, w.moe_xs};
@@ -106,6 +106,16 @@ int ensure_workspace(nvllm_handle* h, int T, int n) {
     WS(w.lat_cq, Tc * cq * asz);
     WS(w.lat_gate, Tc * heads * 4);
     WS(w.lat_o, Tc * ol * asz);
+    size_t dch = 0, dhv = 0, dh = 0;
+    for (auto& y : h->ll)
+      if (y.s.mixer == NVLLM_MIXER_DELTA) {
+        dch = std::max(dch, (size_t)y.conv_ch);
+        dhv = std::max(dhv, (size_t)y.s.heads * y.s.vdim);
+        dh = std::max(dh, (size_t)y.s.heads);
+      }
+    WS(w.dl_qkv, Tc * dch * 4);
+    WS(w.dl_bg, Tc * 2 * dh * 4);
+    WS(w.dl_o, Tc * dhv * 4);
     for (auto& r : h->ropes) {
       WS(r.cosT, (size_t)Tc * (r.dims / 2) * 4);
       WS(r.sinT, (size_t)Tc * (r.dims / 2) * 4);

@@ -2,8 +2,14 @@
 // (nvllm_create_layered): handle set-up, tensors by checkpoint name, the cache pools and the
 // forward pass of one engine step.
 //
-// Every layer is a parallel block on the fp32 residual stream x:
-//     h = LayerNorm(x) (weight only);  x += mixer(h) + feed_forward(h)
+// Two block styles on the fp32 residual stream x (nvllm_layered_config::block_style):
+//   parallel, pre-norm:      h = LayerNorm(x) (weight only);  x += mixer(h) + feed_forward(h)
+//   sequential, post-norm:   x += RMSNorm(mixer(x));  x += RMSNorm(feed_forward(x))  — the
+//     sublayers read x itself (kept beside the fp32 stream in the activation dtype), the norm
+//     kernel normalises the pending sublayer result and adds it (NormArgs::post).  Mixers of
+//     this style: sliding-window attention (attention_window.cu) and the gated delta rule
+//     (delta.cu); feed-forward W_down relu(W_up x)^2.  Positions enter once, as sinusoids
+//     added to the scaled embedding; the head may be the embedding table itself.
 // Mixer "latent attention" (attention_latent.cu): one fused input projection [W_dq | W_dkv | W_g]
 // of h, RMS-normed latents, the query up projection with W_uk folded in, the absorbed-query
 // attention over the paged latent cache (per-head sigmoid gate applied to its result), the output
@@ -31,10 +37,19 @@ void layered_free(nvllm_handle* h) {
   for (auto& y : h->ll) {
     F(y.norm_w); F(y.w_in); F(y.dq_norm); F(y.dkv_norm); F(y.w_uq); F(y.w_uk); F(y.w_uv); F(y.w_o); F(y.w_q); F(y.w_ov);
     F(y.w1); F(y.w2); F(y.router); F(y.moe_in); F(y.moe_out);
+    F(y.post1_w); F(y.post2_w); F(y.conv_w); F(y.a_log); F(y.dt_bias); F(y.onorm_w);
   }
   h->ll.clear();
   for (void* p : h->lat_pools) F(p);
   h->lat_pools.clear();
+  for (void* p : h->win_kpools) F(p);
+  for (void* p : h->win_vpools) F(p);
+  h->win_kpools.clear();
+  h->win_vpools.clear();
+  F(h->pos_freq);
+  h->pos_freq = nullptr;
+  F(h->state_pool);
+  h->state_pool = nullptr;
   for (auto& r : h->ropes) {
     F(r.inv_freq); F(r.cosT); F(r.sinT);
   }
@@ -49,7 +64,12 @@ struct Dst {
   int64_t rows = 0, cols = 0;  // expected shape ([rows] when cols == 0)
   int ld = 0;            // destination row stride (elements)
   int row_mul = 1, row_add = 0;
+  float add = 0.f;       // vectors: constant added to every element (norm weights stored around zero)
 };
+__global__ void add_const_kernel(float* p, size_t n, float c) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] += c;
+}
 }  // namespace
 
 static bool parse_layer_name(const std::string& name, int* layer, std::string* rest) {
@@ -81,10 +101,34 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
   };
   int l = -1;
   std::string rest;
+  const float noff = h->norm_offset;
   if (name == "embed") mat(h->wte, h->V, W, W);
-  else if (name == "head") mat(h->lm_head, h->V, W, W);
-  else if (name == "final.norm") vec(h->lnf_w, W);
-  else if (parse_layer_name(name, &l, &rest) && l < h->L) {
+  else if (name == "head" && h->lm_head_owned) mat(h->lm_head, h->V, W, W);
+  else if (name == "final.norm") { vec(h->lnf_w, W); d.add = noff; }
+  else if (parse_layer_name(name, &l, &rest) && l < h->L && h->ll[l].s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
+    // sequential post-norm blocks: window attention / delta rule mixers, relu^2 feed-forward
+    ListedLayer& y = h->ll[l];
+    const nvllm_layer_spec& s = y.s;
+    const int own = s.kv_from < 0;
+    const bool delta = s.mixer == NVLLM_MIXER_DELTA;
+    if (rest == "norm1") { vec(y.post1_w, W); d.add = noff; }
+    else if (rest == "norm2" && s.mlp != NVLLM_MLP_NONE) { vec(y.post2_w, W); d.add = noff; }
+    else if (rest == "mix.q") mat(y.w_in, y.n_q, W, W, 0);
+    else if (rest == "mix.k" && (delta || own)) mat(y.w_in, y.n_k, W, W, y.n_q);
+    else if (rest == "mix.v" && (delta || own)) mat(y.w_in, y.n_v, W, W, y.n_q + y.n_k);
+    else if (rest == "mix.o") mat(y.w_o, W, (int64_t)s.heads * s.vdim, y.ov_p);
+    else if (delta && rest == "mix.b") mat(y.w_in, s.heads, W, W, y.conv_ch);
+    else if (delta && rest == "mix.a") mat(y.w_in, s.heads, W, W, y.conv_ch + s.heads);
+    else if (delta && rest == "mix.g") mat(y.w_in, (int64_t)s.heads * s.vdim, W, W, y.conv_ch + 2 * s.heads);
+    else if (delta && rest == "mix.q.conv") { mat(y.conv_w, y.n_q, s.conv, s.conv, 0); d.ddt = DT_F32; d.p = y.conv_w; }
+    else if (delta && rest == "mix.k.conv") { mat(y.conv_w, y.n_k, s.conv, s.conv, 0); d.ddt = DT_F32; d.p = y.conv_w + (size_t)y.n_q * s.conv; }
+    else if (delta && rest == "mix.v.conv") { mat(y.conv_w, y.n_v, s.conv, s.conv, 0); d.ddt = DT_F32; d.p = y.conv_w + (size_t)(y.n_q + y.n_k) * s.conv; }
+    else if (delta && rest == "mix.A_log") vec(y.a_log, s.heads);
+    else if (delta && rest == "mix.dt_bias") vec(y.dt_bias, s.heads);
+    else if (delta && rest == "mix.norm") vec(y.onorm_w, s.vdim);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.up") mat(y.w1, s.ff, W, W);
+    else if (s.mlp == NVLLM_MLP_DENSE && rest == "mlp.down") mat(y.w2, W, s.ff, y.ff_p);
+  } else if (parse_layer_name(name, &l, &rest) && l < h->L) {
     ListedLayer& y = h->ll[l];
     const nvllm_layer_spec& s = y.s;
     const int own = s.kv_from < 0;
@@ -128,8 +172,13 @@ int layered_set_weight(nvllm_handle* h, const char* cname, int dtype, const void
   NV_CHECK(h, cudaMalloc(&stage, numel * wire_size(dtype)));
   cudaError_t e = cudaMemcpyAsync(stage, host, numel * wire_size(dtype), cudaMemcpyHostToDevice, h->stream);
   if (e == cudaSuccess) {
-    if (is_vec) e = launch_convert(h->stream, dtype, stage, numel, DT_F32, d.p);
-    else e = launch_copy_rows(h->stream, dtype, stage, (size_t)d.cols, (int)d.rows, (int)d.cols, d.ddt, d.p,
+    if (is_vec) {
+      e = launch_convert(h->stream, dtype, stage, numel, DT_F32, d.p);
+      if (e == cudaSuccess && d.add != 0.f) {
+        add_const_kernel<<<(unsigned)((numel + 255) / 256), 256, 0, h->stream>>>((float*)d.p, numel, d.add);
+        e = cudaGetLastError();
+      }
+    } else e = launch_copy_rows(h->stream, dtype, stage, (size_t)d.cols, (int)d.rows, (int)d.cols, d.ddt, d.p,
                               d.ld, d.row_mul, d.row_add);
   }
   if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
@@ -145,10 +194,25 @@ int layered_finalize(nvllm_handle* h) {
       if (g == n) return true;
     return false;
   };
-  std::vector<std::string> need = {"embed", "head", "final.norm"};
+  std::vector<std::string> need = {"embed", "final.norm"};
+  if (h->lm_head_owned) need.push_back("head");
   for (int l = 0; l < h->L; l++) {
     const nvllm_layer_spec& s = h->ll[l].s;
     const std::string p = "l" + std::to_string(l) + ".";
+    if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
+      for (const char* n : {"norm1", "mix.q", "mix.o"}) need.push_back(p + n);
+      if (s.mixer == NVLLM_MIXER_DELTA) {
+        for (const char* n : {"mix.k", "mix.v", "mix.q.conv", "mix.k.conv", "mix.v.conv", "mix.b", "mix.a", "mix.A_log",
+                              "mix.dt_bias", "mix.norm", "mix.g"})
+          need.push_back(p + n);
+      } else if (s.kv_from < 0) {
+        need.push_back(p + "mix.k");
+        need.push_back(p + "mix.v");
+      }
+      if (s.mlp == NVLLM_MLP_DENSE)
+        for (const char* n : {"norm2", "mlp.up", "mlp.down"}) need.push_back(p + n);
+      continue;
+    }
     for (const char* n : {"norm1", "mix.dq", "mix.dq.norm", "mix.uq", "mix.uk", "mix.uv", "mix.g", "mix.o"})
       need.push_back(p + n);
     if (s.kv_from < 0) {
@@ -170,6 +234,7 @@ int layered_finalize(nvllm_handle* h) {
   for (int l = 0; l < h->L; l++) {
     ListedLayer& y = h->ll[l];
     const nvllm_layer_spec& s = y.s;
+    if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) continue;
     cudaError_t e = launch_latent_fold(h->stream, h->wdt, y.w_uq, y.w_uk, y.w_q, y.w_o, y.w_uv, y.w_ov, h->H, s.heads,
                                        s.dim, s.rot_dim, s.vdim, s.kv_rank, s.q_rank, y.q_rank_p, y.ov_p, y.ovr_p);
     if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
@@ -185,9 +250,40 @@ int layered_finalize(nvllm_handle* h) {
   }
   // cache pools: one per layer with its own down projection, rows [c | rotated key part]
   h->lat_pools.assign(h->L, nullptr);
+  h->win_kpools.assign(h->L, nullptr);
+  h->win_vpools.assign(h->L, nullptr);
   for (int l = 0; l < h->L; l++) {
     ListedLayer& y = h->ll[l];
-    if (y.s.kv_from >= 0) continue;
+    if (y.s.mixer != NVLLM_MIXER_WINDOW_ATTENTION || y.s.kv_from >= 0) continue;
+    // K [blocks][kv_heads][256][dim], V [blocks][kv_heads][256][vdim]
+    const size_t rows = (size_t)h->num_blocks * y.s.kv_heads * KV_BLOCK;
+    const size_t kb = rows * y.s.dim * dt_size(h->kvdt), vb = rows * y.s.vdim * dt_size(h->kvdt);
+    cudaError_t e = cudaMalloc(&h->win_kpools[l], kb);
+    if (e == cudaSuccess) e = cudaMalloc(&h->win_vpools[l], vb);
+    if (e != cudaSuccess)
+      return set_err(h, NVLLM_ERR_NOMEM, "K / V cache of %d blocks does not fit: %s", h->num_blocks, cudaGetErrorString(e));
+    NV_CHECK(h, cudaMemsetAsync(h->win_kpools[l], 0, kb, h->stream));
+    NV_CHECK(h, cudaMemsetAsync(h->win_vpools[l], 0, vb, h->stream));
+    h->kv_bytes += kb + vb;
+  }
+  if (h->state_slot_floats) {
+    const size_t bytes = (size_t)h->num_state_slots * h->state_slot_floats * 4;
+    cudaError_t e = cudaMalloc((void**)&h->state_pool, bytes);
+    if (e != cudaSuccess)
+      return set_err(h, NVLLM_ERR_NOMEM, "recurrent state of %d slots does not fit: %s", h->num_state_slots, cudaGetErrorString(e));
+    NV_CHECK(h, cudaMemsetAsync(h->state_pool, 0, bytes, h->stream));
+    h->kv_bytes += bytes;
+  }
+  if (h->position_kind == NVLLM_LPOS_SINUSOIDAL) {
+    const int half = h->H / 2;
+    std::vector<double> f(half);
+    for (int i = 0; i < half; i++) f[i] = pow(10000.0, -2.0 * (double)i / (double)h->H);
+    NV_CHECK(h, cudaMalloc((void**)&h->pos_freq, (size_t)half * 8));
+    NV_CHECK(h, cudaMemcpy(h->pos_freq, f.data(), (size_t)half * 8, cudaMemcpyHostToDevice));
+  }
+  for (int l = 0; l < h->L; l++) {
+    ListedLayer& y = h->ll[l];
+    if (y.s.mixer != NVLLM_MIXER_LATENT_ATTENTION || y.s.kv_from >= 0) continue;
     const size_t bytes = (size_t)h->num_blocks * KV_BLOCK * y.Dk * dt_size(h->kvdt);
     cudaError_t e = cudaMalloc(&h->lat_pools[l], bytes);
     if (e != cudaSuccess)
@@ -209,6 +305,150 @@ int layered_finalize(nvllm_handle* h) {
   return NVLLM_OK;
 }
 
+
+// ------------------------------------------------------------------ sequential post-norm blocks
+// x += w * rmsnorm(pending sublayer result); xn = x in the activation dtype (what the next
+// sublayer reads)
+static int run_postnorm(nvllm_handle* h, Pending* p, const float* w, int T) {
+  NormArgs a{};
+  a.post = 1;
+  a.x = h->ws.x;
+  a.p1 = p->p; a.S1 = p->S; a.stride1 = p->stride; a.m1 = 1.f;
+  a.w = w; a.eps = h->cfg.norm_eps; a.y = h->ws.xn; a.ydt = h->adt;
+  a.n_rows = T; a.H = h->H;
+  ProfScope ps(h, NVLLM_K_NORM, (double)T * h->H * (4 * 3 + dt_size(h->adt)), 0, (double)T * h->H * 4 * (p->S - 1));
+  LAUNCH(h, launch_norm(h->stream, a));
+  *p = Pending();
+  return NVLLM_OK;
+}
+
+static int mixer_window_attention(nvllm_handle* h, const ListedLayer& y, Pending* out) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = L.T, H = h->H;
+  const int32_t* d = L.d;
+  const double asz = dt_size(h->adt), kvsz = dt_size(h->kvdt);
+  const int own = s.kv_from < 0;
+  int rc;
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  WinAttnArgs a{};
+  a.T = T; a.n_seqs = L.n; a.H = s.heads; a.G = s.kv_heads; a.dim = s.dim; a.vdim = s.vdim;
+  a.window = s.window; a.sink = s.sink; a.qk_norm = s.qk_norm; a.own_kv = own;
+  a.eps = h->cfg.norm_eps; a.scale = s.scale;
+  a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
+  a.slots = d + L.slots;
+  a.kpool = h->win_kpools[y.pool]; a.vpool = h->win_vpools[y.pool];
+  a.q = w.q; a.out = w.attn_out; a.o_ld = y.ov_p;
+  a.block_tables = d + L.block_tables; a.max_blocks = L.max_blocks;
+  a.cu_q = d + L.cu_q; a.seq_start = d + L.seq_start; a.seq_len = d + L.seq_len;
+  if (L.prefill) {
+    a.tile_seq = d + L.tile_seq; a.tile_q0 = d + L.tile_q0; a.n_tiles = L.n_qtiles; a.qtile = h->attn_qtile;
+  } else {
+    a.n_tiles = L.n; a.qtile = 1;
+  }
+  {
+    ProfScope ps(h, NVLLM_K_ROPE_KV,
+                 (double)T * y.n_in * 4 + (double)T * (s.heads * s.dim * asz + own * s.kv_heads * (s.dim + s.vdim) * kvsz), 0,
+                 (double)T * y.n_in * 4 * (pin.S - 1));
+    LAUNCH(h, launch_winattn_prep(h->stream, h->adt, h->kvdt, a));
+  }
+  {
+    // algorithmic: the window's K / V rows of every sequence once per step; flops over the visible pairs
+    const double win = s.window > 0 ? s.window : 1e30;
+    const double keys = std::min((double)L.sum_len, (double)L.n * (win - 1) + (double)T);
+    const double pairs = std::min(L.attn_pairs, (double)T * win);
+    ProfScope ps(h, L.prefill ? NVLLM_K_ATTN_PREFILL : NVLLM_K_ATTN_DECODE, keys * s.kv_heads * (s.dim + s.vdim) * kvsz,
+                 2.0 * s.heads * (s.dim + s.vdim) * pairs, (double)T * (s.heads * s.dim + y.ov_p) * asz);
+    LAUNCH(h, launch_winattn(h->stream, h->adt, h->kvdt, a));
+  }
+  return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+static int mixer_delta(nvllm_handle* h, const ListedLayer& y, Pending* out) {
+  const StepLayout& L = h->lay;
+  Workspace& w = h->ws;
+  const nvllm_layer_spec& s = y.s;
+  const int T = L.T, H = h->H;
+  const int32_t* d = L.d;
+  const double asz = dt_size(h->adt);
+  int rc;
+  Pending pin;
+  if ((rc = run_gemm(h, w.xn, H, y.w_in, T, y.n_in, H, 1.f, w.ws_a, w.ws_a_floats, y.n_in, &pin))) return rc;
+  DeltaArgs a{};
+  a.T = T; a.n_seqs = L.n; a.H = s.heads; a.G = s.kv_heads; a.dim = s.dim; a.vdim = s.vdim; a.taps = s.conv;
+  a.n_q = y.n_q; a.n_k = y.n_k; a.n_v = y.n_v; a.conv_ch = y.conv_ch;
+  a.eps = h->cfg.norm_eps;
+  a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
+  a.conv_w = y.conv_w; a.a_log = y.a_log; a.dt_bias = y.dt_bias; a.onorm_w = y.onorm_w;
+  a.cu_q = d + L.cu_q; a.positions = d + L.positions; a.state_slots = d + L.state_slots;
+  a.state_pool = h->state_pool; a.slot_floats = h->state_slot_floats; a.state_off = y.state_off; a.tail_off = y.tail_off;
+  a.qkv = w.dl_qkv; a.bg = w.dl_bg; a.o = w.dl_o;
+  a.out = w.attn_out; a.o_ld = y.ov_p;
+  const double hv = (double)s.heads * s.vdim;
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * (y.conv_ch + 2 * s.heads) * 8, 0,
+                 (double)T * y.n_in * 4 * (pin.S - 1) + (double)T * y.conv_ch * 4 * (s.conv - 1));
+    LAUNCH(h, launch_delta_prep(h->stream, a));
+  }
+  {
+    // algorithmic: every sequence's state once in and once out, the token inputs once, the read-outs once
+    const double state = (double)L.n * s.heads * s.dim * s.vdim * 4 * 2;
+    ProfScope ps(h, NVLLM_K_RECUR, state + (double)T * (y.conv_ch + 2 * s.heads + hv) * 4, 6.0 * T * hv * s.dim);
+    LAUNCH(h, launch_delta_scan(h->stream, a));
+  }
+  {
+    ProfScope ps(h, NVLLM_K_RECUR, (double)T * hv * (4 + 4 + asz), 0, (double)T * hv * 4 * (pin.S - 1));
+    LAUNCH(h, launch_delta_out(h->stream, h->adt, a));
+  }
+  return run_gemm(h, w.attn_out, y.ov_p, y.w_o, T, H, y.ov_p, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+// W_down act(W_up x), act = relu^2: the activation rides in the up projection's epilogue (tcgen05,
+// no split-K), in the down projection's GEMV pre-stage (steps of <= 8 rows) or in its own kernel
+static int ffn_dense_unary(nvllm_handle* h, const ListedLayer& y, Pending* out) {
+  Workspace& w = h->ws;
+  const int T = h->lay.T, H = h->H, ff = y.ff_p;
+  const double asz = dt_size(h->adt);
+  int rc;
+  Pending h1;
+  if ((rc = run_gemm(h, w.xn, H, y.w1, T, ff, H, 1.f, w.ws_a, w.ws_a_floats, ff, &h1, TC5_EPI_RELU2, w.hbuf, ff, nullptr)))
+    return rc;
+  const char* gpre_env = getenv("NVLLM_GEMV_PRE");
+  if (h1.S > 0 && T <= 8 && !(gpre_env && atoi(gpre_env) == 0)) {
+    GemvPre ga{};
+    ga.mode = 2; ga.hp = h1.p; ga.Sh = h1.S; ga.hstride = h1.stride; ga.hld = ff; ga.swiglu = 2;
+    return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, out, 0, nullptr, 0, nullptr, nullptr, 0,
+                    0.0, nullptr, nullptr, &ga);
+  }
+  if (h1.S > 0) {
+    ProfScope ps(h, NVLLM_K_ACT, (double)T * ff * (4 + asz), 0, (double)T * ff * 4 * (h1.S - 1));
+    LAUNCH(h, launch_act(h->stream, h->adt, T, ff, h1.p, h1.S, h1.stride, nullptr, 2, w.hbuf));
+  }
+  return run_gemm(h, w.hbuf, ff, y.w2, T, H, ff, 1.f, w.ws_b, w.ws_b_floats, H, out);
+}
+
+static int forward_layers_postnorm(nvllm_handle* h) {
+  const int T = h->lay.T;
+  int rc;
+  for (int l = 0; l < h->L; l++) {
+    const ListedLayer& y = h->ll[l];
+    Pending pm;
+    if (y.s.mixer == NVLLM_MIXER_WINDOW_ATTENTION) rc = mixer_window_attention(h, y, &pm);
+    else if (y.s.mixer == NVLLM_MIXER_DELTA) rc = mixer_delta(h, y, &pm);
+    else rc = set_err(h, NVLLM_ERR_INVALID, "layer %d: this mixer has no sequential post-norm form", l);
+    if (rc) return rc;
+    if ((rc = run_postnorm(h, &pm, y.post1_w, T))) return rc;
+    if (y.s.mlp == NVLLM_MLP_DENSE) {
+      Pending pf;
+      if ((rc = ffn_dense_unary(h, y, &pf))) return rc;
+      if ((rc = run_postnorm(h, &pf, y.post2_w, T))) return rc;
+    }
+  }
+  return NVLLM_OK;
+}
+
 // ------------------------------------------------------------------ forward pass
 int forward_step_layered(nvllm_handle* h) {
   const StepLayout& L = h->lay;
@@ -221,8 +461,9 @@ int forward_step_layered(nvllm_handle* h) {
   int rc;
   {
     ProfScope ps(h, NVLLM_K_EMBED, (double)T * H * (4 + wsz), 0);
+    const bool seq_style = h->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM;
     LAUNCH(h, launch_embed(st, h->wdt, d + L.tokens, d_pos, h->wte, nullptr, 0, h->cfg.embedding_multiplier,
-                           w.x, T, H));
+                           w.x, T, H, nullptr, nullptr, nullptr, h->pos_freq, seq_style ? w.xn : nullptr));
   }
   for (auto& r : h->ropes) {
     ProfScope ps(h, NVLLM_K_MISC, (double)T * r.dims * 4, 0);
@@ -230,6 +471,9 @@ int forward_step_layered(nvllm_handle* h) {
   }
   Pending p1, p2;
   int routed = 0;  // routed layers so far: picks the half of topk_w this layer writes
+  if (h->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM) {
+    if ((rc = forward_layers_postnorm(h))) return rc;
+  } else
   for (int l = 0; l < h->L; l++) {
     const ListedLayer& y = h->ll[l];
     const nvllm_layer_spec& s = y.s;
@@ -337,7 +581,8 @@ int forward_step_layered(nvllm_handle* h) {
     }
   }
   // final norm + LM head on the rows that were asked for: each sequence's last, then the extra ones
-  if ((rc = run_norm(h, w.x, &p1, &p2, h->lnf_w, nullptr, w.xn_last, nullptr, d + L.last_row, n_out, nullptr, true)))
+  if ((rc = run_norm(h, w.x, &p1, &p2, h->lnf_w, nullptr, w.xn_last, nullptr, d + L.last_row, n_out, nullptr,
+                     h->block_style == NVLLM_LBLOCK_PARALLEL_PRENORM)))
     return rc;
   Pending lg;
   if ((rc = run_gemm(h, w.xn_last, H, h->lm_head, n_out, h->V, H, 1.f, w.logits_p, w.logits_p_floats, h->ldl, &lg, 0,
@@ -378,7 +623,32 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   if (c->precision != NVLLM_PREC_FP32 && c->precision != NVLLM_PREC_BF16) return bad(-1, "precision");
   for (int l = 0; l < c->num_layers; l++) {
     const nvllm_layer_spec& s = layers[l];
+    const bool seq_style = c->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM;
+    if (s.mixer == NVLLM_MIXER_WINDOW_ATTENTION || s.mixer == NVLLM_MIXER_DELTA) {
+      if (!seq_style) return bad(l, "window attention / delta rule mixers need the sequential post-norm block style");
+      if (s.heads <= 0 || s.kv_heads <= 0 || s.dim <= 0 || s.vdim <= 0) return bad(l, "non-positive mixer size");
+      if (s.heads % s.kv_heads) return bad(l, "heads must be a multiple of kv_heads");
+      if (s.mixer == NVLLM_MIXER_DELTA) {
+        if (s.conv < 1 || s.conv > 8) return bad(l, "convolution taps 1..8");
+        if (s.dim > 1024 || s.vdim > 4096 || s.heads > 256) return bad(l, "delta rule: dim <= 1024, vdim <= 4096, heads <= 256");
+        if (s.kv_from >= 0) return bad(l, "a delta rule layer has no cache to borrow");
+      } else {
+        if (s.window < 0) return bad(l, "negative window");
+        if (s.vdim > 512 || s.dim > 1024) return bad(l, "window attention: dim <= 1024, vdim <= 512");
+        if (s.kv_from >= 0) {
+          if (s.kv_from >= l) return bad(l, "kv_from must name an earlier layer");
+          const nvllm_layer_spec& j = layers[s.kv_from];
+          if (j.mixer != NVLLM_MIXER_WINDOW_ATTENTION || j.kv_from >= 0)
+            return bad(l, "kv_from must name an attention layer with projections of its own");
+          if (j.kv_heads != s.kv_heads || j.dim != s.dim || j.vdim != s.vdim) return bad(l, "kv_from layer has other cache sizes");
+        }
+      }
+      if (s.mlp != NVLLM_MLP_NONE && s.mlp != NVLLM_MLP_DENSE) return bad(l, "unknown feed-forward kind");
+      if (s.mlp == NVLLM_MLP_DENSE && (s.ff <= 0 || s.act != NVLLM_FFN_RELU2)) return bad(l, "dense feed-forward: ff > 0, squared-ReLU activation");
+      continue;
+    }
     if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) return bad(l, "unknown mixer kind");
+    if (seq_style) return bad(l, "latent attention needs the parallel pre-norm block style");
     if (s.heads <= 0 || s.dim <= 0 || s.rot_dim <= 0 || s.vdim <= 0 || s.kv_rank <= 0 || s.q_rank <= 0)
       return bad(l, "non-positive mixer size");
     if (s.kv_rank > 512) return bad(l, "kv_rank above 512");
@@ -420,6 +690,12 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   g.max_seq_len = 1 << 30;
   g.attention_type = NVLLM_ATTN_MQA; g.norm_type = NVLLM_NORM_LAYER; g.position_type = NVLLM_POS_ROPE;
   g.activation_type = NVLLM_ACT_SWIGLU; g.block_style = NVLLM_BLOCK_PARALLEL;
+  if (c->block_style == NVLLM_LBLOCK_SEQUENTIAL_POSTNORM) {
+    g.num_kv_heads = layers[0].kv_heads; g.head_dim = layers[0].dim;
+    g.attention_type = NVLLM_ATTN_GQA; g.norm_type = NVLLM_NORM_RMS; g.position_type = NVLLM_POS_NONE;
+    g.activation_type = NVLLM_ACT_GELU; g.block_style = NVLLM_BLOCK_SEQUENTIAL;
+    g.tied_embedding = c->tied_head;
+  }
   g.norm_eps = c->norm_eps; g.embedding_multiplier = c->embedding_scale;
   g.precision = c->precision;
   g.num_kv_blocks = c->num_kv_blocks > 0 ? c->num_kv_blocks : 1024;
@@ -434,6 +710,10 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
   h->parallel = true;
   h->num_blocks = g.num_kv_blocks;
   h->logit_softcap = c->logit_softcap;
+  h->block_style = c->block_style;
+  h->position_kind = c->position;
+  h->norm_offset = c->norm_offset;
+  h->num_state_slots = c->num_state_slots > 0 ? c->num_state_slots : g.max_num_seqs;
   h->spec_enabled = 0;  // the speculative next step is keyed on the uniform models' shapes
   if (const char* env = getenv("NVLLM_SKIP")) h->skip_mask = (unsigned)strtoul(env, nullptr, 0);
   auto fail = [&](cudaError_t ce, const char* what) {
@@ -458,15 +738,61 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
 #define AL(ptr, bytes) \
   if ((e = alloc((void**)&(ptr), (size_t)(bytes))) != cudaSuccess) return fail(e, "cudaMalloc(weights)");
   AL(h->wte, (size_t)h->V * W * wsz);
-  AL(h->lm_head, (size_t)h->V * W * wsz);
-  h->lm_head_owned = true;
+  if (c->tied_head) {
+    h->lm_head = h->wte;  // [V, W] is already K-contiguous: the table itself is the head
+  } else {
+    AL(h->lm_head, (size_t)h->V * W * wsz);
+    h->lm_head_owned = true;
+  }
   AL(h->lnf_w, (size_t)W * 4);
   h->ll.resize(h->L);
-  int qkv_cols = 0, q_cols = 0;
+  int qkv_cols = 0, q_cols = 0, win_qtile = 0;
   for (int l = 0; l < h->L; l++) {
     ListedLayer& y = h->ll[l];
     y.s = layers[l];
     const nvllm_layer_spec& s = y.s;
+    if (s.mixer != NVLLM_MIXER_LATENT_ATTENTION) {
+      const bool delta = s.mixer == NVLLM_MIXER_DELTA;
+      const int own = s.kv_from < 0;
+      y.ov_p = (int)up8((size_t)s.heads * s.vdim);
+      y.ff_p = (int)up8((size_t)std::max(s.ff, 0));
+      y.pool = own ? l : s.kv_from;
+      if (delta) {
+        y.n_q = y.n_k = s.kv_heads * s.dim;
+        y.n_v = s.heads * s.vdim;
+        y.conv_ch = y.n_q + y.n_k + y.n_v;
+        y.n_in = y.conv_ch + 2 * s.heads + s.heads * s.vdim;  // q | k | v | beta | decay | gate
+        y.state_off = h->state_slot_floats;
+        y.tail_off = y.state_off + (size_t)s.heads * s.dim * s.vdim;
+        h->state_slot_floats = y.tail_off + (size_t)(s.conv - 1) * y.conv_ch;
+        AL(y.conv_w, (size_t)y.conv_ch * s.conv * 4);
+        AL(y.a_log, (size_t)s.heads * 4);
+        AL(y.dt_bias, (size_t)s.heads * 4);
+        AL(y.onorm_w, (size_t)s.vdim * 4);
+      } else {
+        y.n_q = s.heads * s.dim;
+        y.n_k = own ? s.kv_heads * s.dim : 0;
+        y.n_v = own ? s.kv_heads * s.vdim : 0;
+        y.n_in = y.n_q + y.n_k + y.n_v;
+        // every prefill tile list of the step is built for one query-tile size: the smallest any layer wants
+        const int qt = winattn_qtile(h->adt, h->kvdt, s.dim, s.vdim);
+        win_qtile = win_qtile ? std::min(win_qtile, qt) : qt;
+      }
+      AL(y.post1_w, (size_t)W * 4);
+      AL(y.w_in, (size_t)y.n_in * W * wsz);
+      AL(y.w_o, (size_t)W * y.ov_p * wsz);
+      if (s.mlp == NVLLM_MLP_DENSE) {
+        AL(y.post2_w, (size_t)W * 4);
+        AL(y.w1, (size_t)y.ff_p * W * wsz);
+        AL(y.w2, (size_t)W * y.ff_p * wsz);
+        h->F = std::max(h->F, y.ff_p);
+      }
+      qkv_cols = std::max(qkv_cols, std::max(y.n_in, y.ff_p));
+      q_cols = std::max(q_cols, std::max(y.n_q, y.ov_p));
+      h->nh = std::max(h->nh, s.heads);
+      h->hd = std::max(h->hd, s.vdim);
+      continue;
+    }
     y.Dk = s.kv_rank + s.rot_dim;
     y.n_in = s.q_rank + (s.kv_from < 0 ? y.Dk : 0) + s.heads;
     y.q_cols = s.heads * (s.dim + s.rot_dim);
@@ -515,6 +841,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
     h->hd = std::max(h->hd, s.kv_rank);
   }
 #undef AL
+  h->attn_qtile = win_qtile ? win_qtile : latent_attn_qtile();
   h->F = std::max(h->F, 8);
   h->nkv = 1;
   h->qkv_cols = qkv_cols;

@@ -117,7 +117,7 @@ gemv_kernel(const AT* __restrict__ A, int lda, const WT* __restrict__ W, int N, 
       float y = 0.f;
       if (k < klen) {
         const int col = ks + k;
-        if (pre.swiglu) {
+        if (pre.swiglu == 1) {
           float g = 0.f, u = 0.f;
           for (int sl = 0; sl < pre.Sh; sl++) {
             const float* hrow = pre.hp + (size_t)sl * pre.hstride + (size_t)m * pre.hld + 2 * col;
@@ -129,7 +129,7 @@ gemv_kernel(const AT* __restrict__ A, int lda, const WT* __restrict__ W, int N, 
           float hsum = 0.f;
           for (int sl = 0; sl < pre.Sh; sl++) hsum += pre.hp[(size_t)sl * pre.hstride + (size_t)m * pre.hld + col];
           if (pre.hbias) hsum += pre.hbias[col];
-          y = gelu_tanh(hsum);
+          y = pre.swiglu == 2 ? relu2(hsum) : gelu_tanh(hsum);
         }
         y = to_f32(from_f32<AT>(y));
       }

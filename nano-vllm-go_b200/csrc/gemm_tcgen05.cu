@@ -690,7 +690,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           cluster_wait_acquire();
         }
       } else {
-        // GELU branch: gelu_tanh(h + b1)   (transformer.go:67-78)
+        // unary branch: gelu_tanh(h + b1) (transformer.go:67-78), or relu(h)^2 for TC5_EPI_RELU2
         const float b = (epi_bias && n_ok) ? epi_bias[n] : 0.f;
         bf16* obase = epi_out + n;
 #pragma unroll 1
@@ -708,13 +708,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
               for (int c = 0; c < 32; c++)
                 op[(size_t)c * epi_ld] =
-                    __float2bfloat16_rn(gelu_tanh(alpha * __uint_as_float(r[c]) + b));
+                    __float2bfloat16_rn(epi == TC5_EPI_RELU2 ? relu2(alpha * __uint_as_float(r[c]) + b)
+                                                             : gelu_tanh(alpha * __uint_as_float(r[c]) + b));
             } else {
 #pragma unroll
               for (int c = 0; c < 32; c++)
                 if (m0 + c0 + c < M)
                   op[(size_t)c * epi_ld] =
-                      __float2bfloat16_rn(gelu_tanh(alpha * __uint_as_float(r[c]) + b));
+                      __float2bfloat16_rn(epi == TC5_EPI_RELU2 ? relu2(alpha * __uint_as_float(r[c]) + b)
+                                                             : gelu_tanh(alpha * __uint_as_float(r[c]) + b));
             }
           }
         }

@@ -55,6 +55,17 @@ struct ListedLayer {
   void *w1 = nullptr, *w2 = nullptr;  // dense feed-forward: [2 ff, W] gate / up interleaved, [W, ff]
   float* router = nullptr;            // [experts, W] fp32
   void *moe_in = nullptr, *moe_out = nullptr;  // [experts, 2 ff, W] interleaved, [experts, W, ff]
+  // ---- sequential post-norm blocks (window attention / delta rule mixers)
+  float *post1_w = nullptr, *post2_w = nullptr;  // [W] weight (+ norm_offset) of the norm on the mixer / feed-forward output
+  // window attention: fused projection rows [Q heads | K heads | V heads] (no K / V rows when
+  // the layer borrows a cache), W_o [W, ov_p]; K / V pools of the layer it reads
+  // delta rule: fused projection rows [q | k | v | beta | decay | gate]
+  int n_q = 0, n_k = 0, n_v = 0;   // columns of the q / k / v parts of the fused projection
+  int conv_ch = 0;                 // delta rule: channels of the short convolution (n_q + n_k + n_v)
+  float* conv_w = nullptr;         // [conv_ch, taps] fp32
+  float *a_log = nullptr, *dt_bias = nullptr, *onorm_w = nullptr;  // [heads], [heads], [vdim] fp32
+  size_t state_off = 0;            // floats from a slot's base to this layer's [heads][dim][vdim] state
+  size_t tail_off = 0;             // ... and to its convolution tail [taps - 1][conv_ch]
 };
 struct RopeTable {
   double base = 0;
@@ -76,7 +87,7 @@ struct StepLayout {
   size_t words = 0;  // 4-byte words in use
   // offsets (in words) of each array
   size_t tokens, positions, slots, cu_q, seq_start, seq_len, last_row, block_tables, tile_seq,
-      tile_q0, temperature, uniforms;
+      tile_q0, temperature, uniforms, state_slots;
 };
 
 struct Workspace {
@@ -120,6 +131,9 @@ struct Workspace {
   void* lat_cq = nullptr;     // [T, max q_rank_p] act dtype
   float* lat_gate = nullptr;  // [T, max heads]
   void* lat_o = nullptr;      // [T, max ovr_p] act dtype
+  // delta rule (forward_layered.cu): conv + activation output [T, max conv_ch], per-head step
+  // inputs [T, 2 max heads] (write strength | decay), read-outs [T, max heads * vdim], all fp32
+  float *dl_qkv = nullptr, *dl_bg = nullptr, *dl_o = nullptr;
   float* moe_Y = nullptr;  // [T k, H]
   float* moe_y = nullptr;  // [T, H]
   void* moe_xs = nullptr;  // [T k, H] bf16: normed activations in expert-sorted order
@@ -180,6 +194,19 @@ struct nvllm_handle {
   bool layered = false;
   std::vector<nvllm::ListedLayer> ll;
   std::vector<void*> lat_pools;          // per cache-owning layer: [num_blocks * 256][Dk]
+  // window attention: per cache-owning layer K [num_blocks][kv_heads][256][dim], V [...][vdim]
+  std::vector<void*> win_kpools, win_vpools;
+  int block_style = 0, position_kind = 0;
+  float norm_offset = 0.f;               // added to every norm weight at load
+  double* pos_freq = nullptr;            // sinusoidal positions: 10000^(-2i / W), i < W / 2, on the device
+  int attn_qtile = 16;                   // new tokens per attention tile of a prefill step
+  // recurrent state (delta rule): state_pool[slot][state_slot_floats]; the step's slots come
+  // from nvllm_set_state_slots
+  float* state_pool = nullptr;
+  size_t state_slot_floats = 0;
+  int num_state_slots = 0;
+  std::vector<int32_t> next_state_slots;  // for the next nvllm_run
+  std::vector<int32_t> res_state_slots;   // of the device-resident batch
   std::vector<nvllm::RopeTable> ropes;   // distinct (base, dims) of the layers
   std::vector<std::string> named_got;    // tensors handed in so far (nvllm_set_named_weight)
   float logit_softcap = 0.f;

@@ -27,9 +27,13 @@ constexpr int KV_BLOCK = 256;
 // xb / ssq / g (all or none): also write bf16(row * g) — g = the weight of the RMSNorm that reads
 // the row next — and the row's sum of squares ssq[t] (what a GEMM with a folded RMSNorm reads
 // instead of a normed activation)
+// pos_freq != null: entry 2i of the row gets + sin(pos * pos_freq[i]), entry 2i + 1 + cos of the
+// same (angles in double).  y != null: the row also goes out in the weight dtype (the input of
+// a layer whose sublayers read x itself).
 cudaError_t launch_embed(cudaStream_t st, int wdt, const int* tokens, const int* positions,
                          const void* wte, const void* wpe, int max_pos, float mult, float* x, int T,
-                         int H, void* xb = nullptr, float* ssq = nullptr, const float* g = nullptr);
+                         int H, void* xb = nullptr, float* ssq = nullptr, const float* g = nullptr,
+                         const double* pos_freq = nullptr, void* y = nullptr);
 
 // Variants of the top-k routing rule.  Default (all zero): weights renormalised over the chosen
 // experts (moe.go:88-103).  groups > 0: the experts form `groups` equal groups of neighbours, a
@@ -52,6 +56,9 @@ struct NormArgs {
   size_t stride2;
   float m2;
   const float* bias2;
+  // post != 0: the norm sits on the ADDEND: x <- x + rmsnorm(sum_s p1[s]) * w, y = x unchanged
+  // otherwise (a block whose sublayers read x itself and are normed on their way back)
+  int post;
   const float* w;      // [H]; null = all ones (the weight is folded into the next GEMM)
   const float* b;      // [H] or null => RMSNorm (tensor.go:197)
   int centered;        // b == null but still a LayerNorm: (x - mean) / sqrt(var + eps) * w
@@ -84,6 +91,7 @@ cudaError_t launch_norm(cudaStream_t st, const NormArgs& a);
 // GELU:   out[t,j] = gelu_tanh(h[t,j] + b1[j]) (transformer.go:67-78, tensor.go:181-190)
 // glu_limit > 0 (with swiglu): the clamped gated unit g = min(gate, limit), u = clamp(up, +-limit),
 // out = g * sigmoid(1.702 g) * (u + 1)
+// swiglu == 2: out[t,j] = relu(h[t,j])^2
 cudaError_t launch_act(cudaStream_t st, int odt, int T, int F, const float* h, int S, size_t stride,
                        const float* bias, int swiglu, void* out, float glu_limit = 0.f);
 
@@ -193,7 +201,7 @@ struct GemvPre {
   size_t hstride;
   int hld;
   const float* hbias;  // [K] (GELU branch) or null
-  int swiglu;
+  int swiglu;          // 0 tanh-GELU, 1 gated unit, 2 squared ReLU
   float glu_limit;     // > 0 with swiglu: the clamped gated unit (see launch_act)
 };
 // split-K slices a skinny GEMV will produce for (M,N,K); workspace must hold S*M*N floats
@@ -263,7 +271,8 @@ struct Tc5Args {
   const int* g_tile_rows;
   const int* g_n_tiles;  // [1] on the device
 };
-enum { TC5_EPI_PARTIAL = 0, TC5_EPI_SWIGLU = 1, TC5_EPI_GELU = 2, TC5_EPI_RESID = 3 };
+// TC5_EPI_RELU2: like TC5_EPI_GELU (bf16 activation written, no bias needed) with relu(h)^2
+enum { TC5_EPI_PARTIAL = 0, TC5_EPI_SWIGLU = 1, TC5_EPI_GELU = 2, TC5_EPI_RESID = 3, TC5_EPI_RELU2 = 4 };
 // split-K slices for a TC5_EPI_RESID GEMM: like tc5_splits, but every unit must own an SM
 // (the CTAs of a tile wait for each other); 0 = the shape cannot take the fused epilogue
 int tc5_resid_splits(int M, int N, int K, int sm_count);
@@ -391,6 +400,53 @@ cudaError_t launch_latent_attn(cudaStream_t st, int qdt, int kvdt, const LatentA
 // out[i] = cap * tanh(sum_s p[s * stride + i] / cap)   (cap <= 0: plain sum)
 cudaError_t launch_softcap(cudaStream_t st, const float* p, int S, size_t stride, size_t n, float cap,
                            float* out);
+
+// ---------------------------------------------------------------- attention_window.cu
+// Grouped-query attention over a sliding window of the paged cache, optional softmax sink,
+// optional unweighted RMS norm of q / k per head; every size is a run-time argument.
+struct WinAttnArgs {
+  int T, n_seqs;
+  int H, G, dim, vdim;   // query heads, key / value heads, query-key and value entries per head
+  int window;            // position i sees j with 0 <= i - j < window; 0: every j <= i
+  int sink, qk_norm, own_kv;
+  float eps, scale;
+  // fused projection [Q heads | K heads | V heads] (K / V only with own_kv): split-K partials [S][T][in_ld]
+  const float* in_p; int in_S; size_t in_stride; int in_ld;
+  const int* slots;      // [T] pool row of each new token
+  void *kpool, *vpool;   // [blocks][G][256][dim], [blocks][G][256][vdim], cache dtype
+  void* q;               // [T, H * dim] act dtype
+  void* out;             // [T, o_ld] act dtype, columns past H * vdim written as zeros
+  int o_ld;
+  const int* block_tables; int max_blocks;
+  const int *cu_q, *seq_start, *seq_len, *tile_seq, *tile_q0;  // without a tile list: one query per sequence at seq_len - 1
+  int n_tiles, qtile;
+};
+cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
+cudaError_t launch_winattn(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a);
+// queries per tile of the kernel launch_winattn picks for a prefill step (the host builds the tile list with it)
+int winattn_qtile(int qdt, int kvdt, int dim, int vdim);
+
+// ---------------------------------------------------------------- delta.cu
+// Gated delta rule between its two projections, ragged batch; state per slot in fp32.
+struct DeltaArgs {
+  int T, n_seqs;
+  int H, G, dim, vdim, taps;  // heads, query / key heads, entries per head, convolution taps
+  int n_q, n_k, n_v, conv_ch; // columns of q, k, v in the projection; conv_ch = their sum
+  float eps;
+  // fused projection [q | k | v | beta (H) | decay (H) | gate (H vdim)]: split-K partials [S][T][in_ld]
+  const float* in_p; int in_S; size_t in_stride; int in_ld;
+  const float *conv_w, *a_log, *dt_bias, *onorm_w;  // [conv_ch, taps], [H], [H], [vdim]
+  const int *cu_q, *positions, *state_slots;        // [n_seqs + 1], [T], [n_seqs]
+  float* state_pool;     // [slots][slot_floats]
+  size_t slot_floats, state_off, tail_off;  // this layer's state [H][dim][vdim] and tail [taps - 1][conv_ch] inside a slot
+  float* qkv;            // [T, conv_ch] convolved, activated, normalised
+  float* bg;             // [T, 2 H]     write strength | decay
+  float* o;              // [T, H vdim]  read-outs
+  void* out; int o_ld;   // [T, o_ld] act dtype: input of the output projection
+};
+cudaError_t launch_delta_prep(cudaStream_t st, const DeltaArgs& a);
+cudaError_t launch_delta_scan(cudaStream_t st, const DeltaArgs& a);
+cudaError_t launch_delta_out(cudaStream_t st, int odt, const DeltaArgs& a);
 
 // ---------------------------------------------------------------- mamba.cu
 // Mamba2 block between its two projections (mamba2.go:72-351), ragged batch

@@ -55,6 +55,7 @@ static void plan_layout(StepLayout& L, int T, int n, int max_blocks, int n_qtile
   L.tile_q0 = take(n_qtiles);
   L.temperature = take(n);
   L.uniforms = take(n);
+  L.state_slots = take(n);
   L.words = o;
 }
 
@@ -102,7 +103,9 @@ static int graphed_step(nvllm_handle* h, int slot, Pre pre, bool* used) {
   sig.max_blocks = L.max_blocks;
   if (h->layered) {
     // every layer picks its own key split from (batch, its heads, longest context)
-    for (auto& y : h->ll) sig.n_splits += latent_attn_splits(L.n, y.s.heads, L.max_len, h->sm_count);
+    for (auto& y : h->ll)
+      if (y.s.mixer == NVLLM_MIXER_LATENT_ATTENTION)
+        sig.n_splits += latent_attn_splits(L.n, y.s.heads, L.max_len, h->sm_count);
   } else {
     sig.n_splits = attn_decode_splits(h->adt, h->kvdt, L.n, h->nh, h->nkv, h->hd, L.max_len, h->sm_count);
   }
@@ -247,7 +250,20 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
 
   // ---- pass 1: sizes and validation
   int T = 0, max_blocks = 0, n_qtiles = 0, max_len = 0;
-  const int qtile = h->layered ? latent_attn_qtile() : attn_prefill_qtile(h->adt, h->kvdt, h->hd);
+  const int qtile = h->layered ? h->attn_qtile : attn_prefill_qtile(h->adt, h->kvdt, h->hd);
+  // recurrent mixers: every sequence of the step names its state slot (nvllm_set_state_slots)
+  std::vector<int32_t> sslots;
+  sslots.swap(h->next_state_slots);
+  if (h->state_slot_floats) {
+    if ((int)sslots.size() != n)
+      return set_err(h, NVLLM_ERR_STATE, "this model keeps recurrent state: nvllm_set_state_slots must name the %d sequences' slots before the step (got %d)", n, (int)sslots.size());
+    for (int i = 0; i < n; i++) {
+      if (sslots[i] < 0 || sslots[i] >= h->num_state_slots)
+        return set_err(h, NVLLM_ERR_RANGE, "sequence %d: state slot %d outside the %d slots", i, sslots[i], h->num_state_slots);
+      for (int j = 0; j < i; j++)
+        if (sslots[j] == sslots[i]) return set_err(h, NVLLM_ERR_INVALID, "sequences %d and %d share state slot %d", j, i, sslots[i]);
+    }
+  }
   long long sum_len = 0;
   double pairs = 0;
   for (int i = 0; i < n; i++) {
@@ -343,6 +359,7 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
         s[L.tile_seq + tile] = i;
         s[L.tile_q0 + tile] = q0;
       }
+    s[L.state_slots + i] = h->state_slot_floats ? sslots[i] : 0;
     const float t = temperature ? temperature[i] : 0.f;
     s_temp[i] = t;
     s_uni[i] = (t > 0.f) ? (uniforms ? uniforms[i] : next_uniform(h)) : 0.f;
@@ -433,6 +450,16 @@ extern "C" int nvllm_run(nvllm_handle* h, int n, int is_prefill, const int32_t* 
   return NVLLM_OK;
 }
 
+extern "C" int nvllm_set_state_slots(nvllm_handle* h, const int32_t* slots, int n) {
+  if (!h || n < 0 || (n > 0 && !slots)) return NVLLM_ERR_INVALID;
+  h->next_state_slots.assign(slots, slots + n);
+  return NVLLM_OK;
+}
+extern "C" int nvllm_state_slots(nvllm_handle* h) {
+  if (!h) return 0;
+  return h->state_slot_floats ? h->num_state_slots : 0;
+}
+
 extern "C" int nvllm_request_logits(nvllm_handle* h, const int32_t* rows, int n_rows) {
   if (!h || n_rows < 0 || (n_rows > 0 && !rows)) return NVLLM_ERR_INVALID;
   h->want_rows.assign(rows, rows + n_rows);
@@ -500,6 +527,8 @@ static int resident_step(nvllm_handle* h, nvllm_run_stats* stats, bool* used_gra
     h->launches++;
     if (e != cudaSuccess)
       return set_err(h, NVLLM_ERR_CUDA, "make_decode_state: %s", cudaGetErrorString(e));
+    // the sequences keep their state slots
+    NV_CHECK(h, cudaMemcpyAsync(d + D.state_slots, s + L.state_slots, (size_t)n * 4, cudaMemcpyDeviceToDevice, st));
     D.prefill = false;
     D.max_len = L.max_len + 1;
     D.sum_len = L.sum_len + n;

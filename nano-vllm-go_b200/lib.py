@@ -42,7 +42,7 @@ class ProfileEntry(ctypes.Structure):
 
 
 KERNEL_CLASSES = ["embed", "norm", "gemm_tc5", "gemv", "gemm_simt", "rope_kv", "attn_prefill",
-                  "attn_decode", "act", "moe_route", "moe_gemm", "moe_misc", "sample", "misc", "comm"]
+                  "attn_decode", "act", "moe_route", "moe_gemm", "moe_misc", "sample", "misc", "comm", "recur"]
 
 
 class NvllmError(RuntimeError):
@@ -94,6 +94,8 @@ SIGNATURES = {
                                               ctypes.c_int]),
     "nvllm_request_logits": (ctypes.c_int, [ctypes.c_void_p, _i32p, ctypes.c_int]),
     "nvllm_fetch_logits": (ctypes.c_int, [ctypes.c_void_p, _f32p, ctypes.c_int]),
+    "nvllm_set_state_slots": (ctypes.c_int, [ctypes.c_void_p, _i32p, ctypes.c_int]),
+    "nvllm_state_slots": (ctypes.c_int, [ctypes.c_void_p]),
     "nvllm_set_graphs": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "nvllm_set_speculation": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
     "nvllm_get_config": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(C.CConfig)]),

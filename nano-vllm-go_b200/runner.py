@@ -44,7 +44,8 @@ class CudaModelRunner:
                  max_num_seqs: int = 512, max_batched_tokens: int = 16384,
                  weight_dtype: Optional[int] = None, tp_size: int = 1, tp_rank: int = 0,
                  tp_id: Optional[bytes] = None, sampling: Optional[dict] = DEFAULT_SAMPLING,
-                 model_dir: Optional[str] = None, arch: Optional[int] = None):
+                 model_dir: Optional[str] = None, arch: Optional[int] = None,
+                 num_state_slots: int = 0):
         """Replaces NewTensorModelRunner(modelDir) (tensor_model_runner.go:21-32): instead of a
         directory, takes the tensors in the layouts LoadModel leaves them in
         (generic_loader.go:184-265), as (weight_id, layer, ndarray) triples.
@@ -64,14 +65,18 @@ class CudaModelRunner:
         model_dir + arch (config.ARCH_*): what NewTensorModelRunner really takes — the library
         reads model.safetensors / the sharded index itself (nvllm_load_safetensors: mmap, file
         dtype kept, the loader's transposes and QKV splits done on the device); `weights` is
-        then ignored and may be None."""
+        then ignored and may be None.
+
+        num_state_slots: models with recurrent mixers (cfg.needs_state_slots) keep that many
+        sequences' state on the device (0 = max_num_seqs); the engine's block manager hands the
+        slots out (Sequence.state_slot) and Run passes them along."""
         self._lib = L.load()
         self.cfg = cfg
         self.precision = precision
         self._h = ctypes.c_void_p()
         if isinstance(cfg, C.ListedModelConfig):
             self._init_listed(cfg, weights, precision, num_kv_blocks, device, max_num_seqs,
-                              max_batched_tokens, weight_dtype, sampling, model_dir)
+                              max_batched_tokens, weight_dtype, sampling, model_dir, num_state_slots)
             return
         cc = cfg.to_c(precision, num_kv_blocks=num_kv_blocks, max_num_seqs=max_num_seqs,
                       max_batched_tokens=max_batched_tokens, device=device, tp_size=tp_size,
@@ -113,12 +118,13 @@ class CudaModelRunner:
         self.last_logits: Optional[np.ndarray] = None
 
     def _init_listed(self, cfg, weights, precision, num_kv_blocks, device, max_num_seqs,
-                     max_batched_tokens, weight_dtype, sampling, model_dir):
+                     max_batched_tokens, weight_dtype, sampling, model_dir, num_state_slots=0):
         """A model given as a list of layers (config.ListedModelConfig): nvllm_create_layered,
         tensors by checkpoint name — `weights` yields (name, ndarray) pairs, or the library
         reads model_dir's safetensors itself."""
         cc, specs = cfg.to_c(precision, num_kv_blocks=num_kv_blocks, max_num_seqs=max_num_seqs,
-                             max_batched_tokens=max_batched_tokens, device=device)
+                             max_batched_tokens=max_batched_tokens, device=device,
+                             num_state_slots=num_state_slots)
         L.check(self._lib.nvllm_create_layered(ctypes.byref(cc), specs, ctypes.byref(self._h)))
         self.loaded_bytes, self.loaded_tensors = 0, 0
         try:
@@ -183,15 +189,21 @@ class CudaModelRunner:
             [s.token_ids for s in seqs], is_prefill,
             num_cached=[s.num_cached_tokens for s in seqs],
             block_tables=[s.block_table for s in seqs],
-            temperature=[self.temperature] * len(seqs))
+            temperature=[self.temperature] * len(seqs),
+            state_slots=[s.state_slot for s in seqs] if self.needs_state_slots else None)
         return [int(t) for t in toks]
 
     def run_flat(self, token_lists: Seq[Seq[int]], is_prefill: bool,
                  num_cached: Optional[Seq[int]] = None,
                  block_tables: Seq[Seq[int]] = (), temperature: Optional[Seq[float]] = None,
-                 uniforms: Optional[Seq[float]] = None, want_logits: bool = False):
-        """The flattened call of include/nvllm.h::nvllm_run. Returns (tokens[n], logits[n,V]|None)."""
+                 uniforms: Optional[Seq[float]] = None, want_logits: bool = False,
+                 state_slots: Optional[Seq[int]] = None):
+        """The flattened call of include/nvllm.h::nvllm_run. Returns (tokens[n], logits[n,V]|None).
+        state_slots: per sequence, where a model with recurrent mixers keeps its state."""
         n = len(token_lists)
+        if state_slots is not None:
+            ss = np.asarray(state_slots, dtype=np.int32)
+            L.check(self._lib.nvllm_set_state_slots(self._h, L._ip(ss), len(ss)), self._h)
         cu = np.zeros(n + 1, dtype=np.int32)
         np.cumsum([len(t) for t in token_lists], out=cu[1:])
         flat = np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists]) if n else \
@@ -214,6 +226,10 @@ class CudaModelRunner:
         L.check(rc, self._h)
         self.last_logits = logits
         return out, logits
+
+    @property
+    def needs_state_slots(self) -> bool:
+        return bool(getattr(self.cfg, "needs_state_slots", False))
 
     def request_logits(self, rows: Seq[int]) -> None:
         """Ask the next run for the logits of these rows of the step (indices into its computed

@@ -9,7 +9,8 @@ portions beside single decoded tokens; nvllm_run computes tokens [num_cached, le
 sequence), writes the logits at the wanted places of a step to <out>/<step>.f32
 (little-endian fp32, [wanted, vocab]) and prints "done <step>".  Nothing is sampled.  Cache
 blocks come from the engine's block manager and go back to it when a request ends, so a pool
-sized for the live requests is used again and again.
+sized for the live requests is used again and again; models with recurrent mixers also get one
+of MAX_LIVE state slots per live request from it.
 """
 from __future__ import annotations
 
@@ -24,15 +25,19 @@ from . import config as C
 from . import runner as R
 
 
+MAX_LIVE = 4  # requests that are live at any time
+
+
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, echo=print) -> int:
     from harness import go_engine as G
 
     block = C.KV_BLOCK_SIZE
-    # up to four live requests, each may leave one block partly used
-    num_blocks = (max_tokens + block - 1) // block + 4
+    # up to MAX_LIVE live requests, each may leave one block partly used
+    num_blocks = (max_tokens + block - 1) // block + MAX_LIVE
     prec = C.PREC_BF16 if dtype == "bfloat16" else C.PREC_FP32
-    run = R.CudaModelRunner.from_dir(model_dir, precision=prec, num_kv_blocks=num_blocks, sampling=None)
-    bm = G.BlockManager(num_blocks, block)
+    run = R.CudaModelRunner.from_dir(model_dir, precision=prec, num_kv_blocks=num_blocks, sampling=None,
+                                     num_state_slots=MAX_LIVE)
+    bm = G.BlockManager(num_blocks, block, MAX_LIVE if run.needs_state_slots else 0)
     live, done = {}, {}
     os.makedirs(out_dir, exist_ok=True)
     try:
@@ -65,7 +70,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, ech
                 # (key splits, replayed graph); anything else is a ragged prefill step
                 decode = all(len(s) - c == 1 and c > 0 for s, c in zip(seqs, cached))
                 run.run_flat([s.token_ids for s in seqs], not decode, num_cached=cached,
-                             block_tables=[s.block_table for s in seqs], temperature=[0.0] * len(seqs))
+                             block_tables=[s.block_table for s in seqs], temperature=[0.0] * len(seqs),
+                             state_slots=[s.state_slot for s in seqs] if run.needs_state_slots else None)
                 if rows:
                     logits = run.fetch_logits(len(rows))
                     tmp = os.path.join(out_dir, ".%d.tmp" % step["step"])
