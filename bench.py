@@ -485,6 +485,68 @@ def dugopel_device_weights(cfg, device, seed=1234):
         del t
 
 
+def zozonex_cfg(width, n_layers, vocab, d_heads, d_kv, d_dim, d_vdim, conv, a_heads, a_kv, a_dim, window, ff, share=0):
+    """Delta-rule and window-attention layers in turn, every layer with a squared-ReLU feed-forward.
+    share > 0: of every `share` consecutive attention layers only the first has its own K / V cache."""
+    layers, owners = [], []
+    for l in range(n_layers):
+        if l % 2 == 0:
+            kw = dict(mixer=C.MIXER_DELTA, heads=d_heads, kv_heads=d_kv, dim=d_dim, vdim=d_vdim, conv=conv)
+        else:
+            k = l // 2
+            src = owners[k - k % share] if share and k % share else -1
+            owners.append(l)
+            kw = dict(mixer=C.MIXER_WINDOW_ATTENTION, heads=a_heads, kv_heads=a_kv, dim=a_dim, vdim=a_dim, window=window,
+                      sink=1, qk_norm=1, scale=float(a_dim ** -0.5), kv_from=src)
+        kw.update(mlp=C.MLP_DENSE, ff=ff, act=C.FFN_RELU2)
+        layers.append(C.LayerSpec(**kw))
+    return C.ListedModelConfig("zozonex", vocab, width, tuple(layers), 1e-5, embedding_scale=float(width ** 0.5),
+                               arch=C.ARCH_ZOZONEX, block_style=C.LBLOCK_SEQUENTIAL_POSTNORM,
+                               position=C.LPOS_SINUSOIDAL, tied_head=True, norm_offset=1.0)
+
+
+def zozonex_device_weights(cfg, device, seed=1234):
+    import torch
+    g = torch.Generator(device=f"cuda:{device}")
+    for i, (name, shape) in enumerate(cfg.tensor_shapes().items()):
+        g.manual_seed(seed * 1000003 + i)
+        t = torch.empty(shape, dtype=torch.float32, device=f"cuda:{device}")
+        if name.endswith("A_log"):
+            t.uniform_(-3.0, 0.5, generator=g)
+        elif name.endswith("dt_bias"):
+            t.uniform_(-2.0, 1.0, generator=g)
+        elif name.endswith("mix.norm"):
+            t.normal_(1.0, 0.02, generator=g)
+        elif len(shape) == 1:
+            t.normal_(0.0, 0.02, generator=g)  # norm weights are stored around zero
+        else:
+            t.normal_(0.0, 0.02 if name == "embed" else shape[1] ** -0.5, generator=g)
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        del t
+
+
+# width 2048, 16 layers (8 delta rule: 16 heads of 128 x 128 state, 8 query / key heads, 4 taps;
+# 8 window attention: 32 heads of 64 over 8 K / V heads), feed-forward 12288 in every layer
+# (2 matrices: the parameters of Llama's 3 x 8192), vocabulary 128256, head = embedding table
+ZOZONEX_SIZES = {
+    "z-1b": (lambda: zozonex_cfg(2048, 16, 128256, 16, 8, 128, 128, 4, 32, 8, 64, 1024, 12288), "llama-3.2-1b", 64, 512, 128),
+    "z-1b-long": (lambda: zozonex_cfg(2048, 16, 128256, 16, 8, 128, 128, 4, 32, 8, 64, 1024, 12288, share=2),
+                  "llama-3.2-1b", 16, 4096, 64),
+    "z-1b-batch": (lambda: zozonex_cfg(2048, 16, 128256, 16, 8, 128, 128, 4, 32, 8, 64, 1024, 12288), "llama-3.2-1b", 128,
+                   2048, 32),
+}
+
+def hybrid_1b():
+    """Mamba2 and attention blocks in turn at the width and depth of the sizes above: the library's
+    other model with a recurrent mixer (its scan, convolution and gated norm are the kernels the
+    delta rule's stand beside)."""
+    from dataclasses import replace
+    cfg = C.tiny_hybrid(vocab_size=128256, hidden=2048, num_layers=16, num_heads=32, num_kv_heads=8, head_dim=64,
+                        ffn_dim=8192, max_seq_len=8192, mamba_num_heads=64, mamba_head_dim=64, mamba_state_size=128,
+                        mamba_n_groups=8, mamba_conv_kernel=4, hybrid_layers=tuple(l % 2 == 0 for l in range(16)))
+    return replace(cfg, name="hybrid-mamba2-1b")
+
+
 DESIGN_SIZES = {
     # name: (layer-listed config, closest uniform preset, batch, prompt, decode steps)
     "dense-1b": (lambda: dugopel_cfg(2048, 16, 32, 64, 32, 64, 128, 768, 8192, 128256), "llama-3.2-1b", 64, 512, 128),
@@ -506,22 +568,28 @@ def design_bench(args):
     device = 0
     peaks = load_peaks()
     R = nvllm_pkg.sub("runner")
-    out = {"design": "dugopel", "dtype": "bf16", "data": "synthetic (random-init weights, random prompts)",
+    design = args.design
+    sizes = ZOZONEX_SIZES if design == "zozonex" else DESIGN_SIZES
+    gen = zozonex_device_weights if design == "zozonex" else dugopel_device_weights
+    out = {"design": design, "dtype": "bf16", "data": "synthetic (random-init weights, random prompts)",
            "steps": args.steps, "warmup": args.warmup, "peaks": peaks, "sizes": {}}
-    names = [n for n in DESIGN_SIZES if args.design_size in (None, n)]
+    names = [n for n in sizes if args.design_size in (None, n)]
     for name in names:
-        mk, base_name, batch, P, D = DESIGN_SIZES[name]
+        mk, base_name, batch, P, D = sizes[name]
         entry = {"batch": batch, "prompt_len": P, "decode_steps": D}
-        for which in ("dugopel", base_name):
-            cfg = mk() if which == "dugopel" else C.PRESETS[base_name]()
-            if which != "dugopel" and cfg.max_seq_len < P + D + 1:
+        others = (base_name, "hybrid-mamba2-1b") if design == "zozonex" and not args.no_hybrid else (base_name,)
+        for which in (design,) + others:
+            cfg = mk() if which == design else hybrid_1b() if which == "hybrid-mamba2-1b" else C.PRESETS[base_name]()
+            if which != design and cfg.max_seq_len < P + D + 1:
                 from dataclasses import replace
                 cfg = replace(cfg, max_seq_len=P + D + 32)
             job = Job(cfg, batch, P, D, 4321)
-            if which == "dugopel":
-                run = R.CudaModelRunner(cfg, dugopel_device_weights(cfg, device), precision=C.PREC_BF16,
+            if which == design:
+                run = R.CudaModelRunner(cfg, gen(cfg, device), precision=C.PREC_BF16,
                                         num_kv_blocks=job.num_blocks, device=device, max_num_seqs=job.n,
-                                        max_batched_tokens=batch * P, sampling=None)
+                                        max_batched_tokens=batch * P, sampling=None, num_state_slots=job.n)
+                if run.needs_state_slots:
+                    run.set_state_slots(list(range(job.n)))
             else:
                 run = make_runner(cfg, job, device, fast_weights=True)
             run.set_speculation(False)
@@ -572,9 +640,11 @@ def design_bench(args):
 
             mp, md = float(np.median(pre)), float(np.median(dec))
             mem = run.memory_info()
+            state = cfg.state_bytes_per_sequence() if hasattr(cfg, "state_bytes_per_sequence") else 0
             entry[which] = {
                 "params_matmul_M": round(cfg.matmul_params() / 1e6, 1),
-                "cache_bytes_per_token": mem["kv"] // (job.num_blocks * 256),
+                "cache_bytes_per_token": (mem["kv"] - state * job.n) // (job.num_blocks * 256),
+                "state_bytes_per_sequence": state,
                 "prefill_ms": round(mp, 3), "prefill_tok_s": round(batch * P / mp * 1e3),
                 "decode_us_per_step": round(md / D * 1e3, 1), "decode_tok_s": round(batch * D / md * 1e3),
                 "prefill_kernels": classes(prof_p, 1), "decode_kernels": classes(prof_d, D)}
@@ -600,10 +670,11 @@ def main():
     ap.add_argument("--no-profile", action="store_true")
     ap.add_argument("--no-tp", action="store_true",
                     help="skip the Falcon-7B tensor-parallel leg (configs[3] at tp = --gpus)")
-    ap.add_argument("--design", default=None, choices=["dugopel"],
+    ap.add_argument("--design", default=None, choices=["dugopel", "zozonex"],
                     help="instead of the default workload: the layer-listed design beside the closest "
                          "uniform model at equal size (prefill and decode, per-kernel roofline)")
-    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES))
+    ap.add_argument("--no-hybrid", action="store_true", help="--design zozonex: skip the Mamba2 hybrid baseline")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES) + sorted(ZOZONEX_SIZES))
     args = ap.parse_args()
     if args.design:
         return design_bench(args)

@@ -22,6 +22,8 @@
 //    64 queries x one head per CTA, K / V tiles of 64 keys by cp.async (double buffered).
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "mma.cuh"
@@ -37,8 +39,12 @@ __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, 
 }  // namespace
 
 // ------------------------------------------------------------------ projection epilogue
-// grid (T), 256 threads; warps take the heads of the row in turn: H query heads, then (own
-// cache only) G key heads and G value heads
+// grid (T, Y), 256 threads; a warp takes one head of the row at a time: H query heads, then (own
+// cache only) G key heads and G value heads.  A head of up to 256 entries is read once into
+// registers (the split-K slices summed on the way), normed and written; longer heads take two
+// passes over the slices.
+constexpr int WP_MAXV = 8;  // entries per lane kept in registers
+
 template <typename QT, typename KT>
 __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace tr) {
   TRACE_ENTRY(tr);
@@ -50,29 +56,54 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
   const float* row = a.in_p + (size_t)t * a.in_ld;
   const int slot = a.slots[t];
   const int blk = slot / KV_BLOCK, off = slot % KV_BLOCK;
-  for (int it = warp; it < n_items; it += nw) {
+  for (int it = blockIdx.y * nw + warp; it < n_items; it += gridDim.y * nw) {
     int col, n, kind;  // 0 = query, 1 = key, 2 = value
     if (it < a.H) { kind = 0; n = a.dim; col = it * a.dim; }
     else if (it < a.H + a.G) { kind = 1; n = a.dim; col = a.H * a.dim + (it - a.H) * a.dim; }
     else { kind = 2; n = a.vdim; col = (a.H + a.G) * a.dim + (it - a.H - a.G) * a.vdim; }
+    const bool in_regs = n <= 32 * WP_MAXV;
+    float v[WP_MAXV];
+#pragma unroll
+    for (int c = 0; c < WP_MAXV; c++) v[c] = 0.f;
     float ss = 0.f;
-    for (int i = lane; i < n; i += 32) {
-      const float v = sum_slices(row + col + i, a.in_S, a.in_stride);
-      ss += v * v;
+    if (in_regs) {
+#pragma unroll 4
+      for (int sl = 0; sl < a.in_S; sl++) {
+        const float* p = row + (size_t)sl * a.in_stride + col + lane;
+#pragma unroll
+        for (int c = 0; c < WP_MAXV; c++)
+          if (lane + 32 * c < n) v[c] += p[32 * c];
+      }
+#pragma unroll
+      for (int c = 0; c < WP_MAXV; c++) ss += v[c] * v[c];
+    } else {
+      for (int i = lane; i < n; i += 32) {
+        const float x = sum_slices(row + col + i, a.in_S, a.in_stride);
+        ss += x * x;
+      }
     }
     float inv = 1.f;
     if (kind != 2 && a.qk_norm) inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + a.eps);
-    if (kind == 0) {
-      QT* dst = (QT*)a.q + (size_t)t * a.H * a.dim + col;
-      for (int i = lane; i < n; i += 32) dst[i] = from_f32<QT>(sum_slices(row + col + i, a.in_S, a.in_stride) * inv);
-    } else if (kind == 1) {
-      const int g = it - a.H;
-      KT* dst = (KT*)a.kpool + (((size_t)blk * a.G + g) * KV_BLOCK + off) * a.dim;
-      for (int i = lane; i < n; i += 32) dst[i] = from_f32<KT>(sum_slices(row + col + i, a.in_S, a.in_stride) * inv);
+    QT* qd = nullptr;
+    KT* kd = nullptr;
+    if (kind == 0) qd = (QT*)a.q + (size_t)t * a.H * a.dim + col;
+    else if (kind == 1) kd = (KT*)a.kpool + (((size_t)blk * a.G + (it - a.H)) * KV_BLOCK + off) * a.dim;
+    else kd = (KT*)a.vpool + (((size_t)blk * a.G + (it - a.H - a.G)) * KV_BLOCK + off) * a.vdim;
+    if (in_regs) {
+#pragma unroll
+      for (int c = 0; c < WP_MAXV; c++) {
+        const int i = lane + 32 * c;
+        if (i < n) {
+          if (qd) qd[i] = from_f32<QT>(v[c] * inv);
+          else kd[i] = from_f32<KT>(v[c] * inv);
+        }
+      }
     } else {
-      const int g = it - a.H - a.G;
-      KT* dst = (KT*)a.vpool + (((size_t)blk * a.G + g) * KV_BLOCK + off) * a.vdim;
-      for (int i = lane; i < n; i += 32) dst[i] = from_f32<KT>(sum_slices(row + col + i, a.in_S, a.in_stride));
+      for (int i = lane; i < n; i += 32) {
+        const float x = sum_slices(row + col + i, a.in_S, a.in_stride) * inv;
+        if (qd) qd[i] = from_f32<QT>(x);
+        else kd[i] = from_f32<KT>(x);
+      }
     }
   }
   TRACE_EXIT(tr);
@@ -80,10 +111,14 @@ __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace 
 
 cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs& a) {
   if (a.T <= 0) return cudaSuccess;
+  // few rows (decode): the heads of a row spread over several CTAs
+  const int n_items = a.H + (a.own_kv ? 2 * a.G : 0);
+  const int ny = a.T >= 1024 ? 1 : ceil_div(n_items, 8);
+  const dim3 grid(a.T, ny);
   if (qdt == DT_F32 && kvdt == DT_F32)
-    (void)launch_k(winattn_prep_kernel<float, float>, dim3(a.T), dim3(256), 0, st, a, next_trace(30));
+    (void)launch_k(winattn_prep_kernel<float, float>, grid, dim3(256), 0, st, a, next_trace(30));
   else if (qdt == DT_BF16 && kvdt == DT_BF16)
-    (void)launch_k(winattn_prep_kernel<bf16, bf16>, dim3(a.T), dim3(256), 0, st, a, next_trace(30));
+    (void)launch_k(winattn_prep_kernel<bf16, bf16>, grid, dim3(256), 0, st, a, next_trace(30));
   else
     return cudaErrorInvalidValue;
   return cudaGetLastError();
@@ -318,6 +353,189 @@ __global__ void __launch_bounds__(128) winattn_decode_kernel(WinAttnArgs a, Trac
   TRACE_EXIT(tr);
 }
 
+// Grouped decode kernel (dim a multiple of 8, vdim = 32 * VPT): CTA = (sequence, key / value head,
+// chunk of up to GQMAX query heads of its group), so a cached row is read once for the whole
+// group.  A lane scores its own key against all the group's queries with 16-byte loads of the row
+// (queries in shared memory, broadcast), then owns VPT neighbouring value columns: a value row
+// is one coalesced load for the warp, the lanes' probabilities and row addresses travel by shuffle.
+template <int N, typename T>
+__device__ __forceinline__ void load_n(const T* p, float (&v)[N]);
+template <> __device__ __forceinline__ void load_n<1, float>(const float* p, float (&v)[1]) { v[0] = p[0]; }
+template <> __device__ __forceinline__ void load_n<2, float>(const float* p, float (&v)[2]) {
+  const float2 x = *reinterpret_cast<const float2*>(p);
+  v[0] = x.x; v[1] = x.y;
+}
+template <> __device__ __forceinline__ void load_n<4, float>(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <> __device__ __forceinline__ void load_n<8, float>(const float* p, float (&v)[8]) { load8(p, v); }
+template <> __device__ __forceinline__ void load_n<1, bf16>(const bf16* p, float (&v)[1]) { v[0] = __bfloat162float(p[0]); }
+template <> __device__ __forceinline__ void load_n<2, bf16>(const bf16* p, float (&v)[2]) {
+  const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  v[0] = x.x; v[1] = x.y;
+}
+template <> __device__ __forceinline__ void load_n<4, bf16>(const bf16* p, float (&v)[4]) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  v[0] = x.x; v[1] = x.y; v[2] = y.x; v[3] = y.y;
+}
+template <> __device__ __forceinline__ void load_n<8, bf16>(const bf16* p, float (&v)[8]) { load8(p, v); }
+
+constexpr int WD_WARPS = 8;
+template <typename QT, typename KT, int VPT, int GQMAX>
+__global__ void __launch_bounds__(256) winattn_decode_group_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float smem[];
+  const int dim = a.dim, vdim = 32 * VPT;
+  const int seq = blockIdx.x, g = blockIdx.y;
+  const int GQ = a.H / a.G;
+  const int gq0 = blockIdx.z * GQMAX;         // first query head of the chunk within the group
+  const int gqn = min(GQMAX, GQ - gq0);
+  const int h0 = g * GQ + gq0;
+  float* qs = smem;                            // [GQMAX][dim], scaled
+  float* part = smem + GQMAX * dim;            // [WD_WARPS][GQMAX][vdim + 2]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int qp = a.seq_len[seq] - 1;
+  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const KT* kpool = (const KT*)a.kpool;
+  const KT* vpool = (const KT*)a.vpool;
+  for (int i = threadIdx.x; i < gqn * dim; i += blockDim.x)
+    qs[i] = to_f32(((const QT*)a.q)[(size_t)seq * a.H * dim + (size_t)(h0 + i / dim) * dim + i % dim]) * a.scale;
+  __syncthreads();
+  float m[GQMAX], l[GQMAX], acc[GQMAX][VPT];
+#pragma unroll
+  for (int q = 0; q < GQMAX; q++) {
+    m[q] = -INFINITY;
+    l[q] = 0.f;
+#pragma unroll
+    for (int c = 0; c < VPT; c++) acc[q][c] = 0.f;
+  }
+  for (int k0 = k_lo + warp * 32; k0 <= qp; k0 += WD_WARPS * 32) {
+    const int j = k0 + lane;
+    const bool vis = j <= qp;
+    const int jc = vis ? j : qp;
+    const int rowb = (bt[jc / KV_BLOCK] * a.G + g) * KV_BLOCK + (jc % KV_BLOCK);  // row of the layer's pools
+    float s[GQMAX];
+#pragma unroll
+    for (int q = 0; q < GQMAX; q++) s[q] = 0.f;
+    const KT* kr = kpool + (size_t)rowb * dim;
+#pragma unroll 4
+    for (int i = 0; i < dim; i += 8) {
+      float k8[8];
+      load8(kr + i, k8);
+#pragma unroll
+      for (int q = 0; q < GQMAX; q++)
+        if (q < gqn) {
+          const float4 qa = *reinterpret_cast<const float4*>(qs + q * dim + i);
+          const float4 qb = *reinterpret_cast<const float4*>(qs + q * dim + i + 4);
+          s[q] = fmaf(k8[0], qa.x, s[q]); s[q] = fmaf(k8[1], qa.y, s[q]);
+          s[q] = fmaf(k8[2], qa.z, s[q]); s[q] = fmaf(k8[3], qa.w, s[q]);
+          s[q] = fmaf(k8[4], qb.x, s[q]); s[q] = fmaf(k8[5], qb.y, s[q]);
+          s[q] = fmaf(k8[6], qb.z, s[q]); s[q] = fmaf(k8[7], qb.w, s[q]);
+        }
+    }
+    float p[GQMAX];
+#pragma unroll
+    for (int q = 0; q < GQMAX; q++) {
+      const float sv = vis ? s[q] : -INFINITY;
+      const float mn = fmaxf(m[q], warp_max(sv));  // lane 0 of a chunk is always visible
+      const float corr = (m[q] == -INFINITY) ? 0.f : expf(m[q] - mn);
+      p[q] = vis ? expf(sv - mn) : 0.f;
+      l[q] = l[q] * corr + warp_sum(p[q]);
+#pragma unroll
+      for (int c = 0; c < VPT; c++) acc[q][c] *= corr;
+      m[q] = mn;
+    }
+    // weighted sum over the value rows, eight rows in flight at a time; lanes past the last key
+    // carry probability 0 and a valid (clamped) row
+    const int nk = min(32, qp + 1 - k0);
+    for (int jj0 = 0; jj0 < nk; jj0 += 8) {
+      float vv[8][VPT];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int rb = __shfl_sync(0xffffffffu, rowb, jj0 + u);
+        load_n<VPT, KT>(vpool + (size_t)rb * vdim + lane * VPT, vv[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+#pragma unroll
+        for (int q = 0; q < GQMAX; q++) {
+          const float pj = __shfl_sync(0xffffffffu, p[q], jj0 + u);
+#pragma unroll
+          for (int c = 0; c < VPT; c++) acc[q][c] = fmaf(pj, vv[u][c], acc[q][c]);
+        }
+      }
+    }
+  }
+  const int ps = vdim + 2;
+#pragma unroll
+  for (int q = 0; q < GQMAX; q++) {
+    float* mine = part + ((size_t)warp * GQMAX + q) * ps;
+#pragma unroll
+    for (int c = 0; c < VPT; c++) mine[lane * VPT + c] = acc[q][c];
+    if (lane == 0) {
+      mine[vdim] = m[q];
+      mine[vdim + 1] = l[q];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < gqn * vdim; i += blockDim.x) {
+    const int q = i / vdim, col = i % vdim;
+    float mt = a.sink ? 0.f : -INFINITY;
+    for (int w = 0; w < WD_WARPS; w++) mt = fmaxf(mt, part[((size_t)w * GQMAX + q) * ps + vdim]);
+    float lt = a.sink ? expf(0.f - mt) : 0.f, v = 0.f;
+    for (int w = 0; w < WD_WARPS; w++) {
+      const float* pw = part + ((size_t)w * GQMAX + q) * ps;
+      const float cw = (pw[vdim] == -INFINITY) ? 0.f : expf(pw[vdim] - mt);
+      lt += pw[vdim + 1] * cw;
+      v += pw[col] * cw;
+    }
+    ((QT*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + q) * vdim + col] = from_f32<QT>(v / lt);
+  }
+  if (g == 0 && blockIdx.z == 0)
+    for (int col = a.H * vdim + threadIdx.x; col < a.o_ld; col += blockDim.x)
+      ((QT*)a.out)[(size_t)seq * a.o_ld + col] = from_f32<QT>(0.f);
+  TRACE_EXIT(tr);
+}
+
+template <typename QT, typename KT, int VPT>
+static cudaError_t winattn_decode_group_vpt(cudaStream_t st, const WinAttnArgs& a) {
+  const int GQ = a.H / a.G;
+  const int gmax = GQ <= 1 ? 1 : GQ <= 2 ? 2 : GQ <= 4 ? 4 : 8;
+  const dim3 grid(a.n_tiles, a.G, ceil_div(GQ, gmax));
+  const size_t smem = ((size_t)gmax * a.dim + WD_WARPS * (size_t)gmax * (a.vdim + 2)) * sizeof(float);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  if (gmax == 1) (void)launch_k(winattn_decode_group_kernel<QT, KT, VPT, 1>, grid, dim3(32 * WD_WARPS), smem, st, a, next_trace(33));
+  else if (gmax == 2) (void)launch_k(winattn_decode_group_kernel<QT, KT, VPT, 2>, grid, dim3(32 * WD_WARPS), smem, st, a, next_trace(33));
+  else if (gmax == 4) (void)launch_k(winattn_decode_group_kernel<QT, KT, VPT, 4>, grid, dim3(32 * WD_WARPS), smem, st, a, next_trace(33));
+  else (void)launch_k(winattn_decode_group_kernel<QT, KT, VPT, 8>, grid, dim3(32 * WD_WARPS), smem, st, a, next_trace(33));
+  return cudaGetLastError();
+}
+static bool winattn_decode_group_ok(const WinAttnArgs& a) {
+  static const bool on = [] {
+    const char* e = getenv("NVLLM_WINATTN_GROUP");
+    return e ? atoi(e) != 0 : true;
+  }();
+  const int vpt = a.vdim / 32;
+  const int gmax = std::min(8, a.H / a.G);
+  return on && a.dim % 8 == 0 && a.vdim % 32 == 0 && (vpt == 1 || vpt == 2 || vpt == 4 || vpt == 8) &&
+         ((size_t)gmax * a.dim + WD_WARPS * (size_t)gmax * (a.vdim + 2)) * sizeof(float) <= 48 * 1024;
+}
+template <typename QT, typename KT>
+static cudaError_t winattn_decode_group(cudaStream_t st, const WinAttnArgs& a) {
+  switch (a.vdim / 32) {
+    case 1: return winattn_decode_group_vpt<QT, KT, 1>(st, a);
+    case 2: return winattn_decode_group_vpt<QT, KT, 2>(st, a);
+    case 4: return winattn_decode_group_vpt<QT, KT, 4>(st, a);
+    default: return winattn_decode_group_vpt<QT, KT, 8>(st, a);
+  }
+}
+
 template <typename QT, typename KT>
 static cudaError_t winattn_decode_dispatch(cudaStream_t st, const WinAttnArgs& a) {
   const dim3 grid(a.n_tiles, a.H);
@@ -415,7 +633,7 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
   float o[VDIM / 8][4];
 #pragma unroll
   for (int i = 0; i < VDIM / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const float sc = a.scale;
+  const float sc = a.scale * 1.4426950408889634f;  // log2(e): softmax in base 2
 
   for (int kt = 0; kt < n_kt; kt++) {
     const int buf = kt & 1;
@@ -449,19 +667,30 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
           mma16816(s[2 * nb + 1], a0, a1, a2, a3, b2, b3);
         }
       }
-      // scale, mask, running max
+      // scale (scores live in the base-2 domain: exp2 of a difference is one instruction), mask
+      // (only on tiles that some row of the warp sees partly), running max
+      const bool interior = k0 + WM_K - 1 <= w_qlo && k0 + WM_K <= k_hi && (a.window <= 0 || w_qhi - k0 < a.window);
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      if (interior) {
 #pragma unroll
-      for (int nb = 0; nb < WM_K / 8; nb++) {
+        for (int nb = 0; nb < WM_K / 8; nb++) {
+          s[nb][0] *= sc; s[nb][1] *= sc; s[nb][2] *= sc; s[nb][3] *= sc;
+          mx_lo = fmaxf(mx_lo, fmaxf(s[nb][0], s[nb][1]));
+          mx_hi = fmaxf(mx_hi, fmaxf(s[nb][2], s[nb][3]));
+        }
+      } else {
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int j = k0 + nb * 8 + tig * 2 + (e & 1);
-          const int qp = (e & 2) ? qp_hi : qp_lo;
-          const bool vis = j <= qp && j < k_hi && (a.window <= 0 || qp - j < a.window);
-          const float v = vis ? s[nb][e] * sc : -INFINITY;
-          s[nb][e] = v;
-          if (e & 2) mx_hi = fmaxf(mx_hi, v);
-          else mx_lo = fmaxf(mx_lo, v);
+        for (int nb = 0; nb < WM_K / 8; nb++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int j = k0 + nb * 8 + tig * 2 + (e & 1);
+            const int qp = (e & 2) ? qp_hi : qp_lo;
+            const bool vis = j <= qp && j < k_hi && (a.window <= 0 || qp - j < a.window);
+            const float v = vis ? s[nb][e] * sc : -INFINITY;
+            s[nb][e] = v;
+            if (e & 2) mx_hi = fmaxf(mx_hi, v);
+            else mx_lo = fmaxf(mx_lo, v);
+          }
         }
       }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
@@ -470,16 +699,15 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
       // a row that has seen nothing yet (and has no sink) keeps max -inf: every p below is 0
-      const float c_lo = (mn_lo == -INFINITY) ? 1.f : ((m_lo == -INFINITY) ? 0.f : expf(m_lo - mn_lo));
-      const float c_hi = (mn_hi == -INFINITY) ? 1.f : ((m_hi == -INFINITY) ? 0.f : expf(m_hi - mn_hi));
+      const float c_lo = (mn_lo == -INFINITY) ? 1.f : exp2f(m_lo - mn_lo);  // exp2(-inf) = 0
+      const float c_hi = (mn_hi == -INFINITY) ? 1.f : exp2f(m_hi - mn_hi);
+      const float sub_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, sub_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
       float ps_lo = 0.f, ps_hi = 0.f;
       uint32_t pa[WM_K / 8][2];
 #pragma unroll
       for (int nb = 0; nb < WM_K / 8; nb++) {
-        const float p0 = (s[nb][0] == -INFINITY) ? 0.f : expf(s[nb][0] - mn_lo);
-        const float p1 = (s[nb][1] == -INFINITY) ? 0.f : expf(s[nb][1] - mn_lo);
-        const float p2 = (s[nb][2] == -INFINITY) ? 0.f : expf(s[nb][2] - mn_hi);
-        const float p3 = (s[nb][3] == -INFINITY) ? 0.f : expf(s[nb][3] - mn_hi);
+        const float p0 = exp2f(s[nb][0] - sub_lo), p1 = exp2f(s[nb][1] - sub_lo);  // masked scores are -inf: 0
+        const float p2 = exp2f(s[nb][2] - sub_hi), p3 = exp2f(s[nb][3] - sub_hi);
         ps_lo += p0 + p1;
         ps_hi += p2 + p3;
         pa[nb][0] = pack_bf16(p0, p1);
@@ -564,6 +792,10 @@ cudaError_t launch_winattn(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs
   if (a.n_tiles <= 0) return cudaSuccess;
   if (a.H % a.G) return cudaErrorInvalidValue;
   if (a.tile_seq == nullptr) {  // decode: one query per sequence
+    if (winattn_decode_group_ok(a)) {
+      if (qdt == DT_F32 && kvdt == DT_F32) return winattn_decode_group<float, float>(st, a);
+      if (qdt == DT_BF16 && kvdt == DT_BF16) return winattn_decode_group<bf16, bf16>(st, a);
+    }
     if (qdt == DT_F32 && kvdt == DT_F32) return winattn_decode_dispatch<float, float>(st, a);
     if (qdt == DT_BF16 && kvdt == DT_BF16) return winattn_decode_dispatch<bf16, bf16>(st, a);
     return cudaErrorInvalidValue;

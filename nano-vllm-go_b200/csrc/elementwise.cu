@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormArgs a, Trace tr) {
       store8(xr + i, v);
       if (yr) store8(yr + i, v);
     }
+    if (threadIdx.x == 0 && trace_on(tr)) trace_rec(tr, t_entry, t_wait, 0ull);
     return;
   }
   const bool upd = (a.p1 != nullptr) || (a.p2 != nullptr);

@@ -630,7 +630,7 @@ extern "C" int nvllm_create_layered(const nvllm_layered_config* c, const nvllm_l
       if (s.heads % s.kv_heads) return bad(l, "heads must be a multiple of kv_heads");
       if (s.mixer == NVLLM_MIXER_DELTA) {
         if (s.conv < 1 || s.conv > 8) return bad(l, "convolution taps 1..8");
-        if (s.dim > 1024 || s.vdim > 4096 || s.heads > 256) return bad(l, "delta rule: dim <= 1024, vdim <= 4096, heads <= 256");
+        if (s.dim > 512 || s.vdim > 4096 || s.heads > 256) return bad(l, "delta rule: dim <= 512, vdim <= 4096, heads <= 256");
         if (s.kv_from >= 0) return bad(l, "a delta rule layer has no cache to borrow");
       } else {
         if (s.window < 0) return bad(l, "negative window");

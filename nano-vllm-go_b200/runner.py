@@ -202,8 +202,7 @@ class CudaModelRunner:
         state_slots: per sequence, where a model with recurrent mixers keeps its state."""
         n = len(token_lists)
         if state_slots is not None:
-            ss = np.asarray(state_slots, dtype=np.int32)
-            L.check(self._lib.nvllm_set_state_slots(self._h, L._ip(ss), len(ss)), self._h)
+            self.set_state_slots(state_slots)
         cu = np.zeros(n + 1, dtype=np.int32)
         np.cumsum([len(t) for t in token_lists], out=cu[1:])
         flat = np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists]) if n else \
@@ -230,6 +229,11 @@ class CudaModelRunner:
     @property
     def needs_state_slots(self) -> bool:
         return bool(getattr(self.cfg, "needs_state_slots", False))
+
+    def set_state_slots(self, slots: Seq[int]) -> None:
+        """State slots of the next run's sequences (models with recurrent mixers)."""
+        ss = np.asarray(slots, dtype=np.int32)
+        L.check(self._lib.nvllm_set_state_slots(self._h, L._ip(ss), len(ss)), self._h)
 
     def request_logits(self, rows: Seq[int]) -> None:
         """Ask the next run for the logits of these rows of the step (indices into its computed
