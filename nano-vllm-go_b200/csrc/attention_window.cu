@@ -43,9 +43,8 @@ __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, 
 // cache only) G key heads and G value heads.  A head of up to 256 entries is read once into
 // registers (the split-K slices summed on the way), normed and written; longer heads take two
 // passes over the slices.
-constexpr int WP_MAXV = 8;  // entries per lane kept in registers
-
-template <typename QT, typename KT>
+// WP_MAXV: entries per lane kept in registers
+template <typename QT, typename KT, int WP_MAXV>
 __global__ void __launch_bounds__(256) winattn_prep_kernel(WinAttnArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
@@ -115,12 +114,18 @@ cudaError_t launch_winattn_prep(cudaStream_t st, int qdt, int kvdt, const WinAtt
   const int n_items = a.H + (a.own_kv ? 2 * a.G : 0);
   const int ny = a.T >= 1024 ? 1 : ceil_div(n_items, 8);
   const dim3 grid(a.T, ny);
-  if (qdt == DT_F32 && kvdt == DT_F32)
-    (void)launch_k(winattn_prep_kernel<float, float>, grid, dim3(256), 0, st, a, next_trace(30));
-  else if (qdt == DT_BF16 && kvdt == DT_BF16)
-    (void)launch_k(winattn_prep_kernel<bf16, bf16>, grid, dim3(256), 0, st, a, next_trace(30));
-  else
+  const int big = std::max(a.dim, a.vdim);
+  if (qdt == DT_F32 && kvdt == DT_F32) {
+    if (big <= 64) (void)launch_k(winattn_prep_kernel<float, float, 2>, grid, dim3(256), 0, st, a, next_trace(30));
+    else if (big <= 128) (void)launch_k(winattn_prep_kernel<float, float, 4>, grid, dim3(256), 0, st, a, next_trace(30));
+    else (void)launch_k(winattn_prep_kernel<float, float, 8>, grid, dim3(256), 0, st, a, next_trace(30));
+  } else if (qdt == DT_BF16 && kvdt == DT_BF16) {
+    if (big <= 64) (void)launch_k(winattn_prep_kernel<bf16, bf16, 2>, grid, dim3(256), 0, st, a, next_trace(30));
+    else if (big <= 128) (void)launch_k(winattn_prep_kernel<bf16, bf16, 4>, grid, dim3(256), 0, st, a, next_trace(30));
+    else (void)launch_k(winattn_prep_kernel<bf16, bf16, 8>, grid, dim3(256), 0, st, a, next_trace(30));
+  } else {
     return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
 }
 
@@ -385,7 +390,7 @@ template <> __device__ __forceinline__ void load_n<8, bf16>(const bf16* p, float
 
 constexpr int WD_WARPS = 8;
 template <typename QT, typename KT, int VPT, int GQMAX>
-__global__ void __launch_bounds__(256) winattn_decode_group_kernel(WinAttnArgs a, Trace tr) {
+__global__ void __launch_bounds__(256, (GQMAX * VPT <= 16) ? 2 : 1) winattn_decode_group_kernel(WinAttnArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
@@ -420,6 +425,15 @@ __global__ void __launch_bounds__(256) winattn_decode_group_kernel(WinAttnArgs a
     const bool vis = j <= qp;
     const int jc = vis ? j : qp;
     const int rowb = (bt[jc / KV_BLOCK] * a.G + g) * KV_BLOCK + (jc % KV_BLOCK);  // row of the layer's pools
+    // the chunk's value rows do not wait for the scores: the first VB of them are requested now,
+    // beside the key row, and arrive while the scores and the softmax are computed
+    constexpr int VB = (64 / VPT) < 8 ? 8 : ((64 / VPT) > 32 ? 32 : (64 / VPT));  // value rows in flight
+    float vv[VB][VPT];
+#pragma unroll
+    for (int u = 0; u < VB; u++) {
+      const int rb = __shfl_sync(0xffffffffu, rowb, u);
+      load_n<VPT, KT>(vpool + (size_t)rb * vdim + lane * VPT, vv[u]);
+    }
     float s[GQMAX];
 #pragma unroll
     for (int q = 0; q < GQMAX; q++) s[q] = 0.f;
@@ -451,18 +465,19 @@ __global__ void __launch_bounds__(256) winattn_decode_group_kernel(WinAttnArgs a
       for (int c = 0; c < VPT; c++) acc[q][c] *= corr;
       m[q] = mn;
     }
-    // weighted sum over the value rows, eight rows in flight at a time; lanes past the last key
-    // carry probability 0 and a valid (clamped) row
+    // weighted sum over the value rows; lanes past the last key carry probability 0 and a valid
+    // (clamped) row
     const int nk = min(32, qp + 1 - k0);
-    for (int jj0 = 0; jj0 < nk; jj0 += 8) {
-      float vv[8][VPT];
+    for (int jj0 = 0; jj0 < nk; jj0 += VB) {
+      if (jj0 > 0) {
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int rb = __shfl_sync(0xffffffffu, rowb, jj0 + u);
-        load_n<VPT, KT>(vpool + (size_t)rb * vdim + lane * VPT, vv[u]);
+        for (int u = 0; u < VB; u++) {
+          const int rb = __shfl_sync(0xffffffffu, rowb, jj0 + u);
+          load_n<VPT, KT>(vpool + (size_t)rb * vdim + lane * VPT, vv[u]);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
+      for (int u = 0; u < VB; u++) {
 #pragma unroll
         for (int q = 0; q < GQMAX; q++) {
           const float pj = __shfl_sync(0xffffffffu, p[q], jj0 + u);

@@ -50,6 +50,12 @@ __device__ __forceinline__ float sum_slices(const float* __restrict__ p, int S, 
   return acc;
 }
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// SiLU of the convolution outputs and of the output gate: exact in the fp32 mode, fast
+// intrinsics (relative error about 1e-6, far below the bf16 rounding that follows) otherwise
+template <bool FAST>
+__device__ __forceinline__ float silu_t(float x) {
+  return FAST ? __fdividef(x, 1.0f + __expf(-x)) : silu(x);
+}
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -61,7 +67,7 @@ constexpr int DELTA_MAX_TAPS = 8;
 // its own: the G query heads, the G key heads (a unit = one head, whose length the warp needs)
 // and the value channels in pieces of 32 * MAXV; the warps of the row's CTAs take the units in
 // turn.  A lane holds up to MAXV channels of its unit; all their taps' loads are in flight at once.
-template <int MAXV>
+template <int MAXV, bool FAST>
 __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs a, Trace tr) 
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXV; i++) {
-      val[i] = (lane + 32 * i < cn) ? silu(val[i]) : 0.f;
+      val[i] = (lane + 32 * i < cn) ? silu_t<FAST>(val[i]) : 0.f;
       ss += val[i] * val[i];
     }
     float mul = 1.f;
@@ -132,9 +138,15 @@ cudaError_t launch_delta_prep(cudaStream_t st, const DeltaArgs& a) {
   // few rows (decode): a row's units spread over several CTAs
   const int ny = a.T >= 2048 ? 1 : std::min(ceil_div(n_units, 8), std::max(1, 2048 / a.T));
   const dim3 grid(a.T, ny);
-  if (maxv == 4) (void)launch_k(delta_prep_kernel<4>, grid, dim3(256), 0, st, a, next_trace(34));
-  else if (maxv == 8) (void)launch_k(delta_prep_kernel<8>, grid, dim3(256), 0, st, a, next_trace(34));
-  else (void)launch_k(delta_prep_kernel<32>, grid, dim3(256), 0, st, a, next_trace(34));
+  if (a.fast_act) {
+    if (maxv == 4) (void)launch_k(delta_prep_kernel<4, true>, grid, dim3(256), 0, st, a, next_trace(34));
+    else if (maxv == 8) (void)launch_k(delta_prep_kernel<8, true>, grid, dim3(256), 0, st, a, next_trace(34));
+    else (void)launch_k(delta_prep_kernel<32, true>, grid, dim3(256), 0, st, a, next_trace(34));
+  } else {
+    if (maxv == 4) (void)launch_k(delta_prep_kernel<4, false>, grid, dim3(256), 0, st, a, next_trace(34));
+    else if (maxv == 8) (void)launch_k(delta_prep_kernel<8, false>, grid, dim3(256), 0, st, a, next_trace(34));
+    else (void)launch_k(delta_prep_kernel<32, false>, grid, dim3(256), 0, st, a, next_trace(34));
+  }
   return cudaGetLastError();
 }
 
@@ -273,9 +285,10 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a, int LPC, i
 // The same scan with compile-time sizes, dim = R * LPC: lane p of a column holds the R
 // neighbouring rows p R .. p R + R - 1, the keys and queries of a token sit in shared memory as
 // LPC segments of R + 4 floats (the padding puts the lanes' 16-byte reads in different banks),
-// no bounds checks in the token loop, four partial sums per inner product, two CTAs per SM.
-template <int R, int LPC>
-__global__ void __launch_bounds__(256, 2) delta_scan_fixed_kernel(DeltaArgs a, int VC, Trace tr) {
+// no bounds checks in the token loop, four partial sums per inner product; one column per
+// thread and two CTAs per SM, or two columns per thread (CC = 2) and one.
+template <int R, int LPC, int CC>
+__global__ void __launch_bounds__(256, CC == 1 ? 2 : 1) delta_scan_fixed_kernel(DeltaArgs a, int VC, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
   pdl_wait();
@@ -288,9 +301,15 @@ __global__ void __launch_bounds__(256, 2) delta_scan_fixed_kernel(DeltaArgs a, i
   const int start = a.positions[r0];
   float* slot = a.state_pool + (size_t)a.state_slots[s] * a.slot_floats;
   const int tid = threadIdx.x;
-  const int p = tid % LPC, jl = tid / LPC;
-  const int col = vbase + jl;
-  const bool col_ok = jl < VC && col < vdim;
+  const int p = tid % LPC, jl = tid / LPC;  // the thread's CC columns: vbase + jl + cc * (VC / CC)
+  const int VH = VC / CC;
+  bool col_ok[CC];
+  int col[CC];
+#pragma unroll
+  for (int cc = 0; cc < CC; cc++) {
+    col[cc] = vbase + jl + cc * VH;
+    col_ok[cc] = jl < VH && col[cc] < vdim;
+  }
   const int kvh = h / (a.H / a.G);
 
   if (a.taps > 1) {  // roll the convolution tail forward (see the generic kernel)
@@ -314,9 +333,11 @@ __global__ void __launch_bounds__(256, 2) delta_scan_fixed_kernel(DeltaArgs a, i
   }
 
   float* S_g = slot + a.state_off + (size_t)h * DIM * vdim;
-  float S[R];
+  float S[CC][R];
 #pragma unroll
-  for (int r = 0; r < R; r++) S[r] = (start > 0 && col_ok) ? S_g[(size_t)(p * R + r) * vdim + col] : 0.f;
+  for (int cc = 0; cc < CC; cc++)
+#pragma unroll
+    for (int r = 0; r < R; r++) S[cc][r] = (start > 0 && col_ok[cc]) ? S_g[(size_t)(p * R + r) * vdim + col[cc]] : 0.f;
   // tile of DELTA_TT tokens: q [TT][KL], k [TT][KL], v [TT][VC], beta [TT], g [TT]
   const int tile_floats = DELTA_TT * (2 * KL + VC + 2);
   const float* qg = a.qkv + (size_t)kvh * DIM;
@@ -346,8 +367,8 @@ __global__ void __launch_bounds__(256, 2) delta_scan_fixed_kernel(DeltaArgs a, i
   };
   issue(0, 0);
   cp_async_commit();
-  float* og = a.o + (size_t)h * vdim + col;
   const int HV = a.H * vdim;
+  float* og = a.o + (size_t)h * vdim;
   for (int t0 = 0, it = 0; t0 < n_new; t0 += DELTA_TT, it++) {
     const int buf = it & 1;
     if (t0 + DELTA_TT < n_new) issue(t0 + DELTA_TT, buf ^ 1);
@@ -362,59 +383,85 @@ __global__ void __launch_bounds__(256, 2) delta_scan_fixed_kernel(DeltaArgs a, i
     const int nt = min(DELTA_TT, n_new - t0);
     for (int tt = 0; tt < nt; tt++) {
       const float beta = bs[tt], g = bs[DELTA_TT + tt];
-      const float v = col_ok ? vs[tt * VC + jl] : 0.f;
+      float v[CC], dot[CC], out[CC];
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) v[cc] = col_ok[cc] ? vs[tt * VC + jl + cc * VH] : 0.f;
       float kr[R];
-      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+      float d4[CC][4];
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) d4[cc][0] = d4[cc][1] = d4[cc][2] = d4[cc][3] = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * KL + r);
         kr[r] = k4.x; kr[r + 1] = k4.y; kr[r + 2] = k4.z; kr[r + 3] = k4.w;
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          S[r + e] *= g;
-          d4[e] = fmaf(S[r + e], kr[r + e], d4[e]);
-        }
-      }
-      float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        for (int cc = 0; cc < CC; cc++)
 #pragma unroll
-      for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = beta * (v - dot);
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int e = 0; e < 4; e++) {
+            S[cc][r + e] *= g;
+            d4[cc][e] = fmaf(S[cc][r + e], kr[r + e], d4[cc][e]);
+          }
+      }
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        dot[cc] = (d4[cc][0] + d4[cc][1]) + (d4[cc][2] + d4[cc][3]);
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1) dot[cc] += __shfl_xor_sync(0xffffffffu, dot[cc], o);
+        dot[cc] = beta * (v[cc] - dot[cc]);  // u: what the token writes into the column
+        d4[cc][0] = d4[cc][1] = d4[cc][2] = d4[cc][3] = 0.f;
+      }
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * KL + r);
         const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          S[r + e] = fmaf(kr[r + e], u, S[r + e]);
-          o4[e] = fmaf(S[r + e], qv[e], o4[e]);
-        }
-      }
-      float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+        for (int cc = 0; cc < CC; cc++)
 #pragma unroll
-      for (int o = 1; o < LPC; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-      if (p == 0 && col_ok) og[(size_t)(r0 + t0 + tt) * HV] = out;
+          for (int e = 0; e < 4; e++) {
+            S[cc][r + e] = fmaf(kr[r + e], dot[cc], S[cc][r + e]);
+            d4[cc][e] = fmaf(S[cc][r + e], qv[e], d4[cc][e]);
+          }
+      }
+#pragma unroll
+      for (int cc = 0; cc < CC; cc++) {
+        out[cc] = (d4[cc][0] + d4[cc][1]) + (d4[cc][2] + d4[cc][3]);
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1) out[cc] += __shfl_xor_sync(0xffffffffu, out[cc], o);
+        if (p == 0 && col_ok[cc]) og[(size_t)(r0 + t0 + tt) * HV + col[cc]] = out[cc];
+      }
     }
     __syncthreads();  // the buffer may be refilled
   }
   cp_async_wait<0>();
-  if (col_ok) {
 #pragma unroll
-    for (int r = 0; r < R; r++) S_g[(size_t)(p * R + r) * vdim + col] = S[r];
-  }
+  for (int cc = 0; cc < CC; cc++)
+    if (col_ok[cc]) {
+#pragma unroll
+      for (int r = 0; r < R; r++) S_g[(size_t)(p * R + r) * vdim + col[cc]] = S[cc][r];
+    }
   TRACE_EXIT(tr);
 }
 
 template <int R, int LPC>
 static cudaError_t delta_scan_fixed_launch(cudaStream_t st, const DeltaArgs& a) {
-  int VC = 256 / LPC;
+  // two columns per thread (the key / query reads from shared memory, which bound the one-column
+  // form, serve both) when the head has the columns for it
+  static const bool cc2_on = !(getenv("NVLLM_DELTA_CC2") && atoi(getenv("NVLLM_DELTA_CC2")) == 0);
+  const bool cc2 = cc2_on && a.vdim >= 2 * (256 / LPC);
+  int VC = (cc2 ? 2 : 1) * (256 / LPC);
   if (VC > a.vdim) VC = a.vdim;
-  const int threads = (VC * LPC + 31) / 32 * 32;
+  const int threads = cc2 ? 256 : (VC * LPC + 31) / 32 * 32;
   const dim3 grid(a.n_seqs, a.H, ceil_div(a.vdim, VC));
   const size_t smem = (size_t)2 * DELTA_TT * (2 * LPC * (R + 4) + VC + 2) * sizeof(float);
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(delta_scan_fixed_kernel<R, LPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  (void)launch_k(delta_scan_fixed_kernel<R, LPC>, grid, dim3(threads), smem, st, a, VC, next_trace(35));
+  if (cc2) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(delta_scan_fixed_kernel<R, LPC, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(delta_scan_fixed_kernel<R, LPC, 2>, grid, dim3(threads), smem, st, a, VC, next_trace(35));
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(delta_scan_fixed_kernel<R, LPC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    (void)launch_k(delta_scan_fixed_kernel<R, LPC, 1>, grid, dim3(threads), smem, st, a, VC, next_trace(35));
+  }
   return cudaGetLastError();
 }
 
@@ -460,7 +507,7 @@ cudaError_t launch_delta_scan(cudaStream_t st, const DeltaArgs& a) {
 }
 
 // ------------------------------------------------------------------ gated norm of the read-out
-template <typename OT>
+template <typename OT, int MV>
 __global__ void __launch_bounds__(256) delta_out_kernel(DeltaArgs a, Trace tr) {
   TRACE_ENTRY(tr);
   pdl_launch_dependents();
@@ -470,7 +517,8 @@ __global__ void __launch_bounds__(256) delta_out_kernel(DeltaArgs a, Trace tr) {
   const int vdim = a.vdim;
   OT* out = (OT*)a.out + (size_t)t * a.o_ld;
   const float* gate = a.in_p + (size_t)t * a.in_ld + a.conv_ch + 2 * a.H;
-  constexpr int MV = 8;  // heads of up to 256 columns stay in registers: read-outs and gates are loaded together
+  // heads of up to 32 * MV columns stay in registers: read-outs and gates are loaded together
+  constexpr bool FAST = sizeof(OT) == 2;
   for (int h = blockIdx.y * nw + warp; h < a.H; h += gridDim.y * nw) {
     const float* o = a.o + (size_t)t * a.H * vdim + (size_t)h * vdim;
     if (vdim <= 32 * MV) {
@@ -488,7 +536,7 @@ __global__ void __launch_bounds__(256) delta_out_kernel(DeltaArgs a, Trace tr) {
 #pragma unroll
       for (int c = 0; c < MV; c++) {
         const int i = lane + 32 * c;
-        if (i < vdim) out[h * vdim + i] = from_f32<OT>(ov[c] * inv * a.onorm_w[i] * silu(gv[c]));
+        if (i < vdim) out[h * vdim + i] = from_f32<OT>(ov[c] * inv * a.onorm_w[i] * silu_t<FAST>(gv[c]));
       }
       continue;
     }
@@ -508,8 +556,9 @@ __global__ void __launch_bounds__(256) delta_out_kernel(DeltaArgs a, Trace tr) {
 cudaError_t launch_delta_out(cudaStream_t st, int odt, const DeltaArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   const dim3 grid(a.T, a.T >= 1024 ? 1 : ceil_div(a.H, 8));  // few rows (decode): a row's heads spread over several CTAs
-  if (odt == DT_F32) (void)launch_k(delta_out_kernel<float>, grid, dim3(256), 0, st, a, next_trace(36));
-  else (void)launch_k(delta_out_kernel<bf16>, grid, dim3(256), 0, st, a, next_trace(36));
+  if (odt == DT_F32) (void)launch_k(delta_out_kernel<float, 8>, grid, dim3(256), 0, st, a, next_trace(36));
+  else if (a.vdim <= 128) (void)launch_k(delta_out_kernel<bf16, 4>, grid, dim3(256), 0, st, a, next_trace(36));
+  else (void)launch_k(delta_out_kernel<bf16, 8>, grid, dim3(256), 0, st, a, next_trace(36));
   return cudaGetLastError();
 }
 

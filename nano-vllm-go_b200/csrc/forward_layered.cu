@@ -380,6 +380,7 @@ static int mixer_delta(nvllm_handle* h, const ListedLayer& y, Pending* out) {
   a.T = T; a.n_seqs = L.n; a.H = s.heads; a.G = s.kv_heads; a.dim = s.dim; a.vdim = s.vdim; a.taps = s.conv;
   a.n_q = y.n_q; a.n_k = y.n_k; a.n_v = y.n_v; a.conv_ch = y.conv_ch;
   a.eps = h->cfg.norm_eps;
+  a.fast_act = h->adt == DT_BF16;
   a.in_p = pin.p; a.in_S = pin.S; a.in_stride = pin.stride; a.in_ld = y.n_in;
   a.conv_w = y.conv_w; a.a_log = y.a_log; a.dt_bias = y.dt_bias; a.onorm_w = y.onorm_w;
   a.cu_q = d + L.cu_q; a.positions = d + L.positions; a.state_slots = d + L.state_slots;

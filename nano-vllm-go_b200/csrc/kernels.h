@@ -433,6 +433,7 @@ struct DeltaArgs {
   int H, G, dim, vdim, taps;  // heads, query / key heads, entries per head, convolution taps
   int n_q, n_k, n_v, conv_ch; // columns of q, k, v in the projection; conv_ch = their sum
   float eps;
+  int fast_act;          // SiLU of the convolution outputs with fast intrinsics (the bf16 serving mode)
   // fused projection [q | k | v | beta (H) | decay (H) | gate (H vdim)]: split-K partials [S][T][in_ld]
   const float* in_p; int in_S; size_t in_stride; int in_ld;
   const float *conv_w, *a_log, *dt_bias, *onorm_w;  // [conv_ch, taps], [H], [H], [vdim]
