@@ -775,6 +775,200 @@ __global__ void __launch_bounds__(128) winattn_mma_kernel(WinAttnArgs a, Trace t
   TRACE_EXIT(tr);
 }
 
+// ------------------------------------------------------------------ decode on mma.sync (bf16)
+// CTA = (sequence, key / value head), 4 warps.  The 16 rows of the MMA tile are the query heads of
+// the group (all at the sequence's last position; rows past the group are zero), so a cached row
+// is read once for the whole group.  K / V tiles of 64 keys arrive by cp.async in a ring of three
+// (two tiles in flight while one is computed); every warp takes 16 keys of each tile — S = Q K^T
+// on its keys, the running softmax in base 2, O += P V — and the four partial states meet in
+// shared memory at the end, where the sink joins once.
+constexpr int WDM_ST = 3;
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(128) winattn_decode_mma_kernel(WinAttnArgs a, Trace tr) {
+  TRACE_ENTRY(tr);
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int DP = DIM + 8, VP = VDIM + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [16][DP]
+  bf16* Ks = Qs + 16 * DP;                        // [WDM_ST][64][DP]
+  bf16* Vs = Ks + WDM_ST * WM_K * DP;             // [WDM_ST][64][VP]
+  const int seq = blockIdx.x, g = blockIdx.y;
+  const int GQ = a.H / a.G, h0 = g * GQ;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int qp = a.seq_len[seq] - 1;
+  const int k_lo = a.window > 0 ? max(0, qp - a.window + 1) : 0;
+  const int t_lo = k_lo / WM_K * WM_K;
+  const int n_kt = (qp + 1 - t_lo + WM_K - 1) / WM_K;
+  const int* bt = a.block_tables + (size_t)seq * a.max_blocks;
+  const bf16* kpool = (const bf16*)a.kpool;
+  const bf16* vpool = (const bf16*)a.vpool;
+  const bf16* qg = (const bf16*)a.q + ((size_t)seq * a.H + h0) * DIM;  // the group's heads are neighbours
+  for (int i = threadIdx.x; i < 16 * (DIM / 8); i += blockDim.x) {
+    const int r = i / (DIM / 8), c = i % (DIM / 8);
+    const bool ok = r < GQ;
+    cp_async16(smem_addr(Qs + r * DP + c * 8), ok ? (const void*)(qg + (size_t)r * DIM + c * 8) : (const void*)qg, ok);
+  }
+  auto load_kv = [&](int kt) {
+    const int buf = kt % WDM_ST;
+    const int k0 = t_lo + kt * WM_K;
+    const int nk = min(WM_K, qp + 1 - k0);
+    const size_t kb = (((size_t)bt[k0 / KV_BLOCK] * a.G + g) * KV_BLOCK + (k0 % KV_BLOCK));
+    bf16* kd = Ks + buf * WM_K * DP;
+    bf16* vd = Vs + buf * WM_K * VP;
+    for (int i = threadIdx.x; i < WM_K * (DIM / 8); i += blockDim.x) {
+      const int r = i / (DIM / 8), c = i % (DIM / 8);
+      const bool ok = r < nk;
+      cp_async16(smem_addr(kd + r * DP + c * 8), ok ? (const void*)(kpool + (kb + r) * DIM + c * 8) : (const void*)kpool, ok);
+    }
+    for (int i = threadIdx.x; i < WM_K * (VDIM / 8); i += blockDim.x) {
+      const int r = i / (VDIM / 8), c = i % (VDIM / 8);
+      const bool ok = r < nk;
+      cp_async16(smem_addr(vd + r * VP + c * 8), ok ? (const void*)(vpool + (kb + r) * VDIM + c * 8) : (const void*)vpool, ok);
+    }
+  };
+  load_kv(0);
+  cp_async_commit();
+  if (n_kt > 1) load_kv(1);
+  cp_async_commit();
+
+  const int gid = lane >> 2, tig = lane & 3;
+  const int kb16 = warp * 16;  // the warp's keys inside a tile
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float o[VDIM / 8][4];
+#pragma unroll
+  for (int i = 0; i < VDIM / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  uint32_t qa[DIM / 16][4];
+  const float sc = a.scale * 1.4426950408889634f;  // log2(e): softmax in base 2
+
+  for (int kt = 0; kt < n_kt; kt++) {
+    if (kt + 2 < n_kt) load_kv(kt + 2);
+    cp_async_commit();
+    cp_async_wait<2>();  // tile kt (and, the first time, the queries) has landed
+    __syncthreads();
+    if (kt == 0) {
+#pragma unroll
+      for (int kk = 0; kk < DIM / 16; kk++)
+        ldsm_x4(smem_addr(Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+    }
+    const int k0 = t_lo + kt * WM_K;
+    const bf16* kd = Ks + (kt % WDM_ST) * WM_K * DP;
+    const bf16* vd = Vs + (kt % WDM_ST) * WM_K * VP;
+    const int j0 = k0 + kb16;  // first key of the warp's 16
+    if (j0 <= qp && j0 + 15 >= k_lo) {
+      float s[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DIM / 16; kk++) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_addr(kd + (kb16 + (lane & 7) + ((lane >> 4) << 3)) * DP + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+        mma16816(s[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+        mma16816(s[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b2, b3);
+      }
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < 2; nb++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int j = j0 + nb * 8 + tig * 2 + (e & 1);
+          const float v = (j >= k_lo && j <= qp) ? s[nb][e] * sc : -INFINITY;  // every row sits at position qp
+          s[nb][e] = v;
+          if (e & 2) mx_hi = fmaxf(mx_hi, v);
+          else mx_lo = fmaxf(mx_lo, v);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);  // finite: at least one key of the 16 is visible
+      const float c_lo = exp2f(m_lo - mn_lo), c_hi = exp2f(m_hi - mn_hi);  // exp2(-inf) = 0
+      float ps_lo = 0.f, ps_hi = 0.f;
+      uint32_t pa[2][2];
+#pragma unroll
+      for (int nb = 0; nb < 2; nb++) {
+        const float p0 = exp2f(s[nb][0] - mn_lo), p1 = exp2f(s[nb][1] - mn_lo);
+        const float p2 = exp2f(s[nb][2] - mn_hi), p3 = exp2f(s[nb][3] - mn_hi);
+        ps_lo += p0 + p1;
+        ps_hi += p2 + p3;
+        pa[nb][0] = pack_bf16(p0, p1);
+        pa[nb][1] = pack_bf16(p2, p3);
+      }
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
+      l_lo = l_lo * c_lo + ps_lo;
+      l_hi = l_hi * c_hi + ps_hi;
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) {
+        o[i][0] *= c_lo; o[i][1] *= c_lo;
+        o[i][2] *= c_hi; o[i][3] *= c_hi;
+      }
+#pragma unroll
+      for (int nb = 0; nb < VDIM / 16; nb++) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_addr(vd + (kb16 + (lane & 15)) * VP + nb * 16 + (lane >> 4) * 8), b0, b1, b2, b3);
+        mma16816(o[2 * nb], pa[0][0], pa[0][1], pa[1][0], pa[1][1], b0, b1);
+        mma16816(o[2 * nb + 1], pa[0][0], pa[0][1], pa[1][0], pa[1][1], b2, b3);
+      }
+    }
+    __syncthreads();  // the buffer is free for the load of tile kt + 3
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // the four warps' states meet in the (now free) tile buffers: [4][16][VDIM + 2] floats
+  float* mrg = reinterpret_cast<float*>(Ks);
+  constexpr int MS = VDIM + 2;
+  {
+    float* lo = mrg + ((size_t)warp * 16 + gid) * MS;
+    float* hi = mrg + ((size_t)warp * 16 + gid + 8) * MS;
+#pragma unroll
+    for (int i = 0; i < VDIM / 8; i++) {
+      const int col = i * 8 + tig * 2;
+      lo[col] = o[i][0]; lo[col + 1] = o[i][1];
+      hi[col] = o[i][2]; hi[col + 1] = o[i][3];
+    }
+    if (tig == 0) {
+      lo[VDIM] = m_lo; lo[VDIM + 1] = l_lo;
+      hi[VDIM] = m_hi; hi[VDIM + 1] = l_hi;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < GQ * VDIM; i += blockDim.x) {
+    const int r = i / VDIM, col = i % VDIM;
+    float mt = a.sink ? 0.f : -INFINITY;
+    for (int w = 0; w < 4; w++) mt = fmaxf(mt, mrg[((size_t)w * 16 + r) * MS + VDIM]);
+    float lt = a.sink ? exp2f(0.f - mt) : 0.f, v = 0.f;
+    for (int w = 0; w < 4; w++) {
+      const float* pw = mrg + ((size_t)w * 16 + r) * MS;
+      const float cw = exp2f(pw[VDIM] - mt);  // a warp that saw no key has max -inf: weight 0
+      lt += pw[VDIM + 1] * cw;
+      v += pw[col] * cw;
+    }
+    ((bf16*)a.out)[(size_t)seq * a.o_ld + (size_t)(h0 + r) * VDIM + col] = __float2bfloat16_rn(v / lt);
+  }
+  if (g == 0)
+    for (int col = a.H * VDIM + threadIdx.x; col < a.o_ld; col += blockDim.x)
+      ((bf16*)a.out)[(size_t)seq * a.o_ld + col] = __float2bfloat16_rn(0.f);
+  TRACE_EXIT(tr);
+}
+
+template <int DIM, int VDIM>
+static cudaError_t winattn_decode_mma_launch(cudaStream_t st, const WinAttnArgs& a) {
+  const size_t tiles = (size_t)WDM_ST * WM_K * ((DIM + 8) + (VDIM + 8)) * 2;
+  const size_t merge = (size_t)4 * 16 * (VDIM + 2) * 4;
+  const size_t smem = (size_t)16 * (DIM + 8) * 2 + std::max(tiles, merge);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(winattn_decode_mma_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  (void)launch_k(winattn_decode_mma_kernel<DIM, VDIM>, dim3(a.n_tiles, a.G), dim3(128), smem, st, a, next_trace(37));
+  return cudaGetLastError();
+}
+
 static bool winattn_mma_on() {
   static const bool on = [] {
     const char* e = getenv("NVLLM_WINATTN_MMA");
@@ -807,6 +1001,15 @@ cudaError_t launch_winattn(cudaStream_t st, int qdt, int kvdt, const WinAttnArgs
   if (a.n_tiles <= 0) return cudaSuccess;
   if (a.H % a.G) return cudaErrorInvalidValue;
   if (a.tile_seq == nullptr) {  // decode: one query per sequence
+    static const bool dec_mma = !(getenv("NVLLM_WINATTN_DECODE_MMA") && atoi(getenv("NVLLM_WINATTN_DECODE_MMA")) == 0);
+    if (dec_mma && winattn_uses_mma(qdt, kvdt, a.dim, a.vdim) && a.H / a.G <= 16) {
+      if (a.dim == 64 && a.vdim == 64) return winattn_decode_mma_launch<64, 64>(st, a);
+      if (a.dim == 96 && a.vdim == 96) return winattn_decode_mma_launch<96, 96>(st, a);
+      if (a.dim == 128 && a.vdim == 128) return winattn_decode_mma_launch<128, 128>(st, a);
+      if (a.dim == 32 && a.vdim == 32) return winattn_decode_mma_launch<32, 32>(st, a);
+      if (a.dim == 64 && a.vdim == 128) return winattn_decode_mma_launch<64, 128>(st, a);
+      if (a.dim == 128 && a.vdim == 64) return winattn_decode_mma_launch<128, 64>(st, a);
+    }
     if (winattn_decode_group_ok(a)) {
       if (qdt == DT_F32 && kvdt == DT_F32) return winattn_decode_group<float, float>(st, a);
       if (qdt == DT_BF16 && kvdt == DT_BF16) return winattn_decode_group<bf16, bf16>(st, a);
