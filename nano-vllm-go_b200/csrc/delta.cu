@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs a, Trace tr) 
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int s = seq_of_row(a.cu_q, a.n_seqs, t);
+  // one row per sequence (a decode step): row t is sequence t, no search through the offsets
+  const int s = a.T == a.n_seqs ? t : seq_of_row(a.cu_q, a.n_seqs, t);
   const int r0 = a.cu_q[s];
   const int li = t - r0;                 // index among the step's rows of the sequence
   const int pos = a.positions[r0] + li;  // position in the sequence
