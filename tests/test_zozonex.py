@@ -70,6 +70,16 @@ def mma_model():
                   layer(attn(heads=2, kv_heads=2, dim=32, vdim=32, window=200))], width=128)
 
 
+def wide_model():
+    """Groups of 12 query heads on one key / value head (more rows than half an MMA tile, more
+    than one chunk of the grouped fp32 decode kernel), 128-wide heads, query / key and value
+    sizes that differ."""
+    return model([layer(attn(heads=12, kv_heads=1, dim=64, vdim=128, window=90), 64),
+                  layer(delta(heads=2, kv_heads=2, dim=128, vdim=128, conv=2)),
+                  layer(attn(heads=4, kv_heads=2, dim=128, vdim=128, window=300)),
+                  layer(attn(heads=3, kv_heads=3, dim=128, vdim=64, window=33), 96)], width=128)
+
+
 def random_weights(cfg_json, seed, bf16=False):
     cfg = C.zozonex_from_json(cfg_json)
     rng = np.random.default_rng(seed)
@@ -235,9 +245,9 @@ def test_each_mechanism_alone(case, prec):
 
 @gpu
 @pytest.mark.parametrize("prec", PRECS)
-@pytest.mark.parametrize("which", ["mixed", "odd", "mma"])
+@pytest.mark.parametrize("which", ["mixed", "odd", "mma", "wide"])
 def test_prefill_equals_token_by_token_decoding(which, prec):
-    j = {"mixed": mixed_model, "odd": odd_model, "mma": mma_model}[which]()
+    j = {"mixed": mixed_model, "odd": odd_model, "mma": mma_model, "wide": wide_model}[which]()
     cfg, w, eng = setup(j, prec)
     try:
         toks = prompt(j, 70, 2)
